@@ -1,0 +1,92 @@
+/*
+ * trak_b200 -- C ABI of the B200 (sm_100a) implementation of TRAK's two
+ * data-parallel hot paths: the Johnson-Lindenstrauss projection of per-example
+ * gradients and the after-kernel scoring.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every device pointer is memory of `device`
+ *   - the library allocates nothing on the device: outputs and workspaces are
+ *     the caller's, sized with the *_workspace_bytes queries
+ *   - calls enqueue work on `stream` (a cudaStream_t passed as void*) and
+ *     return without waiting; inputs, outputs and workspace must stay alive
+ *     until that work has run
+ *   - return value: TB_OK or a TB_ERR_* code; tb_strerror() names it
+ *   - kernels never wait without a bound; a wait that runs out is recorded in a
+ *     per-device status word that tb_device_status() reads (after a sync)
+ *
+ * Paths named in the comments are relative to the reference checkout
+ * (MadryLab/trak).
+ */
+#ifndef TRAK_B200_H
+#define TRAK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB_OK 0
+#define TB_ERR_BAD_DTYPE 1      /* dtype not one of TB_F16 / TB_BF16 / TB_F32            */
+#define TB_ERR_BAD_SHAPE 2      /* zero or negative extent, ld < F, B out of range ...    */
+#define TB_ERR_BAD_PROJ_DIM 3   /* N is not a positive multiple of 512                    */
+#define TB_ERR_BAD_ARG 4        /* null pointer, unknown proj_type, misaligned output ... */
+#define TB_ERR_WORKSPACE 5      /* workspace missing, misaligned or too small             */
+#define TB_ERR_CUDA 6           /* a CUDA runtime / driver call failed (see tb_last_cuda_error) */
+#define TB_ERR_DEVICE_TIMEOUT 7 /* a bounded wait inside a kernel ran out                 */
+#define TB_ERR_UNSUPPORTED 8    /* not a B200-class device, or size beyond a stated limit */
+
+#define TB_F16 0
+#define TB_BF16 1
+#define TB_F32 2
+
+/* Values follow the reference's enum order (fast_jl/types.cuh:3-6). */
+#define TB_RADEMACHER 0
+#define TB_NORMAL 1
+
+int tb_version(void);
+const char *tb_strerror(int code);
+/* Text of the last CUDA error this thread's calls ran into ("" if none). */
+const char *tb_last_cuda_error(void);
+
+/* Synchronises `device` and returns TB_OK, or TB_ERR_DEVICE_TIMEOUT if any
+ * kernel of this library gave up a wait since the last call (the word is
+ * cleared by the call).  *detail, if not null, receives the raw status word. */
+int tb_device_status(int device, uint32_t *detail);
+
+/* ---- JL projection ---------------------------------------------------------
+ * out[b, n] = alpha * sum_f grads[b, f] * P[f, n]   (+ out[b, n] if accumulate)
+ *
+ * P is the F x N matrix that the reference's fast_jl kernel defines for
+ * (seed, num_feature_tiles, proj_type); it is regenerated on the fly, never
+ * stored.  Replaces fast_jl<p_type, NUM_BATCHES>() (fast_jl/fast_jl.cu:29-79),
+ * project<>() (fast_jl/fast_jl_kernel.cuh:107-132) and project_kernel
+ * (fast_jl/fast_jl_kernel.cuh:24-105), i.e. all six pybind entry points
+ * project_{rademacher,normal}_{8,16,32} (fast_jl/fast_jl.cu:81-110).
+ *
+ *   grads   [B, F] row-major with leading dimension ld (elements), dtype
+ *           TB_F16 / TB_BF16 / TB_F32; fp32 is rounded to fp16 on the way in,
+ *           as the reference does (fast_jl/data_loading.cuh:10)
+ *   out     [B, N] fp32 with leading dimension ld_out, 16-byte aligned rows
+ *   N       positive multiple of 512 (fast_jl/fast_jl_kernel.cuh:113)
+ *   num_feature_tiles  part of the matrix definition (the reference passes the
+ *           SM count, trak/projectors.py:370,409); clamped to F as in
+ *           fast_jl/fast_jl.cu:42
+ *   alpha, accumulate   extras: fold 1/sqrt(D) and sum parameter chunks
+ *           without another pass (trak/traker.py:426, trak/projectors.py:490)
+ *   ws      workspace of at least tb_project_workspace_bytes(...) bytes,
+ *           256-byte aligned; any B is accepted (no 8/16/32 variants)
+ */
+size_t tb_project_workspace_bytes(int dtype, int64_t B, int64_t F, uint32_t N,
+                                  uint32_t num_feature_tiles);
+
+int tb_project(int device, void *stream, const void *grads, int dtype, int64_t B, int64_t F,
+               int64_t ld, float *out, int64_t ld_out, uint32_t N, uint32_t seed,
+               uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate, void *ws,
+               size_t ws_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRAK_B200_H */

@@ -1,0 +1,82 @@
+"""ctypes binding of ``libtrakb200.so`` (the C ABI declared in ``include/trak_b200.h``).
+
+There is no fallback: if the shared library is missing or a call fails, the
+caller gets an exception.
+"""
+import ctypes
+import os
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtrakb200.so")
+
+TB_F16, TB_BF16, TB_F32 = 0, 1, 2
+TB_RADEMACHER, TB_NORMAL = 0, 1
+TB_OK = 0
+TB_ERR_BAD_PROJ_DIM = 3
+TB_ERR_DEVICE_TIMEOUT = 7
+
+_lib = None
+_lock = threading.Lock()
+
+_i, _i64, _u32 = ctypes.c_int, ctypes.c_int64, ctypes.c_uint32
+_vp, _sz, _f = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
+
+# name -> (restype, argtypes); one entry per function include/trak_b200.h declares
+SIGNATURES = {
+    "tb_version": (_i, []),
+    "tb_strerror": (ctypes.c_char_p, [_i]),
+    "tb_last_cuda_error": (ctypes.c_char_p, []),
+    "tb_device_status": (_i, [_i, ctypes.POINTER(_u32)]),
+    "tb_project_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32]),
+    "tb_project": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i,
+                        _vp, _sz]),
+}
+
+
+def lib():
+    """The loaded library.  Raises ImportError (with the build hint) when absent."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise ImportError(
+                    f"{LIB_PATH} not found: build it with `python -m trak_b200.build` "
+                    "(needs nvcc; the kernels are sm_100a only and there is no CPU fallback)")
+            l = ctypes.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(l, name)
+                fn.restype = res
+                fn.argtypes = args
+            _lib = l
+    return _lib
+
+
+class DeviceTimeout(RuntimeError):
+    pass
+
+
+def check(rc: int) -> None:
+    """Maps a status code to the exception type the reference raises for it:
+    ValueError for a bad projection dimension (std::invalid_argument in
+    fast_jl/fast_jl_kernel.cuh:113-115), RuntimeError otherwise."""
+    if rc == TB_OK:
+        return
+    l = lib()
+    msg = l.tb_strerror(rc).decode()
+    if rc == TB_ERR_BAD_PROJ_DIM:
+        raise ValueError(msg)
+    if rc == 6:
+        msg = f"CUDA error: {l.tb_last_cuda_error().decode()}"
+    if rc == TB_ERR_DEVICE_TIMEOUT:
+        raise DeviceTimeout(msg)
+    raise RuntimeError(f"trak_b200: {msg} (code {rc})")
+
+
+def device_status(device: int) -> None:
+    """Synchronises the device and raises DeviceTimeout if a kernel gave up a wait."""
+    detail = _u32(0)
+    rc = lib().tb_device_status(device, ctypes.byref(detail))
+    if rc == TB_ERR_DEVICE_TIMEOUT:
+        raise DeviceTimeout(f"trak_b200: a bounded wait inside a kernel ran out (status {detail.value})")
+    check(rc)

@@ -1,0 +1,119 @@
+"""Drop-in for the reference's ``fast_jl`` extension module.
+
+Same six callables with the same positional signature
+``(input, N, seed, num_feature_tiles) -> float32 CUDA tensor [B, N]``
+(fast_jl/fast_jl.cu:81-110), backed by the sm_100a kernels behind the C ABI.
+The 8 / 16 / 32 suffix (rows per launch in the reference) is only a name here:
+every entry point takes any number of rows and walks the matrix once per 256.
+
+To make an unmodified ``trak`` pick this module up::
+
+    import sys, trak_b200.fast_jl
+    sys.modules["fast_jl"] = trak_b200.fast_jl
+"""
+import os
+
+import torch
+
+from . import _lib
+
+_STRICT = os.environ.get("TRAK_B200_STRICT", "1") != "0"
+_DTYPES = {torch.float16: _lib.TB_F16, torch.bfloat16: _lib.TB_BF16, torch.float32: _lib.TB_F32}
+_workspaces = {}
+
+
+def _u32(name, v):
+    if isinstance(v, bool) or not isinstance(v, int):
+        try:
+            v = v.__index__()
+        except Exception:
+            raise TypeError(f"{name} must be an unsigned 32-bit integer, got {type(v).__name__}")
+    if v < 0 or v > 0xFFFFFFFF:
+        raise TypeError(f"{name} must be an unsigned 32-bit integer, got {v}")
+    return v
+
+
+def _workspace(device, stream, nbytes):
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        _workspaces.pop(key, None)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def free_workspaces():
+    """Drops the cached per-(device, stream) workspaces."""
+    _workspaces.clear()
+
+
+def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None, accumulate=False,
+            strict=None):
+    """``alpha * input @ P`` with the fast_jl matrix P(seed, num_feature_tiles, proj_type).
+
+    ``out`` (float32 [B, N], rows 16-byte aligned) and ``accumulate`` let callers
+    sum parameter chunks in place; ``alpha`` folds a normalisation into the same
+    pass.  With ``strict`` (default: env TRAK_B200_STRICT, on) the call waits for
+    the kernels and raises if one of them gave up a bounded wait.
+    """
+    if not isinstance(input, torch.Tensor) or not input.is_cuda:
+        raise RuntimeError("input must be a CUDA tensor")
+    if not input.is_contiguous():
+        raise RuntimeError("input must be contiguous")
+    if input.dim() != 2:
+        raise RuntimeError("input must be 2D")
+    if input.dtype not in _DTYPES:
+        raise RuntimeError("input must be fp16 or fp32 (bf16 is accepted as well)")
+    N = _u32("N", N)
+    seed = _u32("seed", seed)
+    num_feature_tiles = _u32("num_feature_tiles", num_feature_tiles)
+    B, F = input.shape
+    if B == 0 or F == 0:
+        raise RuntimeError("input must not be empty")
+    l = _lib.lib()
+    dev = input.device
+    if out is None:
+        out = torch.empty((B, N), dtype=torch.float32, device=dev)
+        accumulate = False
+    else:
+        if out.device != dev or out.dtype != torch.float32 or out.dim() != 2 or out.shape[0] != B \
+                or out.shape[1] != N or out.stride(1) != 1:
+            raise RuntimeError("out must be a float32 [B, N] tensor on the input's device")
+    dt = _DTYPES[input.dtype]
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        nbytes = l.tb_project_workspace_bytes(dt, B, F, N, max(num_feature_tiles, 1))
+        ws = _workspace(dev, stream, max(nbytes, 256))
+        rc = l.tb_project(dev.index, stream, input.data_ptr(), dt, B, F, input.stride(0),
+                          out.data_ptr(), out.stride(0), N, seed, num_feature_tiles,
+                          int(proj_type), float(alpha), int(bool(accumulate)), ws.data_ptr(),
+                          ws.numel())
+        _lib.check(rc)
+        if _STRICT if strict is None else strict:
+            _lib.device_status(dev.index)
+    return out
+
+
+def project_rademacher_8(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_RADEMACHER)
+
+
+def project_rademacher_16(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_RADEMACHER)
+
+
+def project_rademacher_32(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_RADEMACHER)
+
+
+def project_normal_8(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
+
+
+def project_normal_16(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
+
+
+def project_normal_32(input, N, seed, num_feature_tiles):
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
