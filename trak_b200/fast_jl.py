@@ -49,20 +49,24 @@ def free_workspaces():
 
 
 def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None, accumulate=False,
-            strict=None):
+            strict=None, allow_strided=False):
     """``alpha * input @ P`` with the fast_jl matrix P(seed, num_feature_tiles, proj_type).
 
     ``out`` (float32 [B, N], rows 16-byte aligned) and ``accumulate`` let callers
     sum parameter chunks in place; ``alpha`` folds a normalisation into the same
     pass.  With ``strict`` (default: env TRAK_B200_STRICT, on) the call waits for
-    the kernels and raises if one of them gave up a bounded wait.
+    the kernels and raises if one of them gave up a bounded wait.  With
+    ``allow_strided`` the rows may be further apart than their length (a column
+    slice of a wider buffer); the six ``project_*`` entry points keep the
+    reference's contiguity check.
     """
     if not isinstance(input, torch.Tensor) or not input.is_cuda:
         raise RuntimeError("input must be a CUDA tensor")
-    if not input.is_contiguous():
-        raise RuntimeError("input must be contiguous")
     if input.dim() != 2:
         raise RuntimeError("input must be 2D")
+    if not input.is_contiguous():
+        if not (allow_strided and input.stride(1) == 1 and input.stride(0) >= input.shape[1]):
+            raise RuntimeError("input must be contiguous")
     if input.dtype not in _DTYPES:
         raise RuntimeError("input must be fp16 or fp32 (bf16 is accepted as well)")
     N = _u32("N", N)

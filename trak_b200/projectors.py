@@ -1,0 +1,157 @@
+"""Projector classes with the reference's constructor and ``project`` signatures,
+running on the sm_100a kernels.
+
+Mirrors ``ProjectionType`` (trak/projectors.py:25-27), ``CudaProjector``
+(trak/projectors.py:317-427) and ``ChunkedCudaProjector``
+(trak/projectors.py:430-516).  They can be handed to an unmodified ``TRAKer``
+through its ``projector=`` argument, or picked up implicitly by registering
+``trak_b200.fast_jl`` as the ``fast_jl`` module.
+"""
+from enum import Enum
+from typing import Union
+
+import torch
+
+from . import fast_jl as _fast_jl
+from . import _lib
+
+
+class ProjectionType(str, Enum):
+    normal: str = "normal"
+    rademacher: str = "rademacher"
+
+
+_PTYPE_CODE = {"rademacher": _lib.TB_RADEMACHER, "normal": _lib.TB_NORMAL}
+
+
+def _ptype_code(proj_type) -> int:
+    name = proj_type.value if isinstance(proj_type, Enum) else str(proj_type)
+    try:
+        return _PTYPE_CODE[name]
+    except KeyError:
+        raise KeyError(f"Projection type {proj_type} not recognized.")
+
+
+def vectorize(g: dict, device="cuda") -> torch.Tensor:
+    """Flattens a dict of per-sample gradients ``{name: [B, *shape]}`` into ``[B, D]`` in
+    dict order; a tensor with fewer than two dimensions contributes one column
+    (trak/utils.py:80-110)."""
+    vals = list(g.values())
+    B = vals[0].shape[0]
+    widths = [1 if v.dim() < 2 else v[0].numel() for v in vals]
+    out = torch.empty((B, sum(widths)), dtype=vals[0].dtype, device=device)
+    ptr = 0
+    for v, w in zip(vals, widths):
+        if v.shape[0] != B:
+            raise AssertionError("all gradients must share the batch dimension")
+        out[:, ptr:ptr + w] = v.data.reshape(B, w).to(device)
+        ptr += w
+    return out
+
+
+class CudaProjector:
+    """JL projection on a B200.  ``max_batch_size`` is accepted for signature
+    compatibility; the kernels take any batch and ignore it."""
+
+    def __init__(self, grad_dim: int, proj_dim: int, seed: int, proj_type: ProjectionType, device,
+                 max_batch_size: int = 32, *args, **kwargs) -> None:
+        self.grad_dim = grad_dim
+        self.proj_dim = proj_dim
+        self.seed = seed
+        self.proj_type = proj_type
+        self.max_batch_size = max_batch_size
+        if isinstance(device, str):
+            device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError("CudaProjector only works on a CUDA device; Either switch to a CUDA "
+                             "device, or use the BasicProjector")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        self._ptype = _ptype_code(proj_type)
+        # the SM count is part of the matrix definition (trak/projectors.py:370,409)
+        self.num_sms = torch.cuda.get_device_properties(device.index).multi_processor_count
+        try:
+            _lib.lib()
+        except ImportError as e:
+            raise ModuleNotFoundError(str(e))
+        # same init-time launch as the reference, on this projector's device
+        _fast_jl.project_rademacher_8(torch.zeros(8, 1_000, device=device), 512, 0, self.num_sms)
+
+    def project(self, grads: Union[dict, torch.Tensor], model_id: int, *, alpha: float = 1.0,
+                out: torch.Tensor = None, accumulate: bool = False) -> torch.Tensor:
+        if isinstance(grads, dict):
+            grads = vectorize(grads, device=self.device)
+        return _fast_jl.project(grads, self.proj_dim, (self.seed + int(1e4) * model_id) & 0xFFFFFFFF,
+                                self.num_sms, self._ptype, alpha=alpha, out=out,
+                                accumulate=accumulate, allow_strided=True)
+
+    def free_memory(self):
+        """Drops the cached kernel workspaces."""
+        _fast_jl.free_workspaces()
+
+
+class ChunkedCudaProjector:
+    """Projects models whose gradient does not fit one call: parameters are packed,
+    whole, into chunks of at most ``max_chunk_size`` features, each chunk has its own
+    projector (own seed), and the chunk projections are summed.
+
+    Differences from the reference that do not change the result beyond fp32
+    round-off: chunks are summed in fp32 inside the kernel's epilogue instead of
+    ``add_`` in the storage dtype, and only the rows of the current batch are
+    projected."""
+
+    def __init__(self, projector_per_chunk: list, max_chunk_size: int, params_per_chunk: list,
+                 feat_bs: int, device: torch.device, dtype: torch.dtype):
+        self.projector_per_chunk = projector_per_chunk
+        self.proj_dim = self.projector_per_chunk[0].proj_dim
+        self.proj_type = self.projector_per_chunk[0].proj_type
+        self.params_per_chunk = params_per_chunk
+        self.max_chunk_size = max_chunk_size
+        self.feat_bs = feat_bs
+        self.device = device
+        self.dtype = dtype
+        self.input_allocated = False
+
+    def allocate_input(self):
+        if self.input_allocated:
+            return
+        width = max(int(c) for c in self.params_per_chunk)
+        self.ch_input = torch.zeros((self.feat_bs, width), device=self.device, dtype=self.dtype)
+        self.input_allocated = True
+
+    def free_memory(self):
+        if not self.input_allocated:
+            return
+        del self.ch_input
+        self.input_allocated = False
+
+    def _flush(self, index, rows, pointer, model_id, out, first):
+        assert pointer == self.params_per_chunk[index]
+        proj = self.projector_per_chunk[index]
+        chunk = self.ch_input[:rows, :pointer]
+        if isinstance(proj, CudaProjector):
+            # row-strided view goes to the kernel as is (leading dimension = buffer width)
+            proj.project(chunk, model_id=model_id, out=out, accumulate=not first)
+        else:  # any other projector object with the reference's project(grads, model_id)
+            res = proj.project(chunk.contiguous(), model_id=model_id).to(torch.float32)
+            out.copy_(res) if first else out.add_(res)
+
+    def project(self, grads, model_id):
+        self.allocate_input()
+        vals = list(grads.values())
+        rows = min(self.feat_bs, vals[0].shape[0])
+        out = torch.empty((rows, self.proj_dim), device=self.device, dtype=torch.float32)
+        pointer, index, first = 0, 0, True
+        for p in vals:
+            flat = p.data.unsqueeze(-1) if p.dim() < 2 else p.data.flatten(start_dim=1)
+            width = flat.size(1)
+            if pointer + width > self.max_chunk_size:
+                self._flush(index, rows, pointer, model_id, out, first)
+                pointer, index, first = 0, index + 1, False
+            # same consistency requirement as the reference's asserts on params_per_chunk
+            assert pointer + width <= self.ch_input.size(1), "params_per_chunk does not match grads"
+            self.ch_input[:rows, pointer:pointer + width].copy_(flat[:rows])
+            pointer += width
+        self._flush(index, rows, pointer, model_id, out, first)
+        return out.to(self.dtype)
