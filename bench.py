@@ -1,0 +1,288 @@
+"""Benchmark of the JL projection hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (per GPU): Gaussian JL projection of 128 per-example gradients of a CIFAR
+ResNet-18 (D = 11,173,962 features, fp16, N(0, 1e-2)) to k = 4096, seed 17,
+148 feature tiles.  One step = one pass of the projection over one such batch.
+Multi-GPU: one process per GPU (torchrun), every rank projects its own batch of
+128 examples with the same virtual matrix -- the path shards by example, there is
+no data-path collective (weak scaling).
+
+Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
+HBM; ``e2e`` is the same through the public ``fast_jl.project_normal_32`` call with
+the batch in pinned host memory and the result read back; ``roofline`` rates the
+projection kernel against the tensor-core peak; ``cpu_baseline`` is the CPU port of
+the reference's BasicProjector timed on a bounded sample on this box.
+
+``--impl reference`` times that CPU port alone (all host threads) on the same
+workload, one bounded sample per step.  ``--scale f`` shrinks D by f (for profiler
+captures of the same command on a small case).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D_FULL = 11_173_962
+ROWS = 128
+K_DIM = 4096
+SEED = 17
+TILES = 148
+BLOCK = 100  # BasicProjector's column block (trak/projectors.py:229)
+
+# DRAM traffic of one projection-kernel launch on the full workload, from the ncu
+# capture summarised in profiles/project_kernel_normal_small.md (dram__bytes_read.sum +
+# dram__bytes_write.sum at D/10, which grows in proportion to D, times 10)
+NCU_TRAFFIC_BYTES_FULL = 3.66e9
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("bf16_tflops_sustained", d.get("bf16_tflops"))), "measured (sustained bf16, MEASURED_PEAKS.json)"
+    return 1400.0, "fallback (sustained bf16 figure of an earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        clocks, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                clocks.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+_cpu_input = {}
+
+
+def cpu_port_sample(rows, D, threads, blocks):
+    """Times the CPU port of BasicProjector on `blocks` of the ceil(k/100) column blocks."""
+    import torch
+    from oracle import basic_ref
+    torch.set_num_threads(threads)
+    if (rows, D) not in _cpu_input:  # the input is made once, outside the timed part
+        _cpu_input.clear()
+        _cpu_input[(rows, D)] = torch.randn(rows, D, generator=torch.Generator().manual_seed(1000)) * 1e-2
+    g = _cpu_input[(rows, D)]
+    t0 = time.perf_counter()
+    basic_ref.basic_project(g, K_DIM, SEED, "normal", blocks=range(blocks))
+    dt = time.perf_counter() - t0
+    nblocks = -(-K_DIM // BLOCK)
+    return dt * nblocks / blocks, dt  # extrapolated full-step seconds, measured seconds
+
+
+def run_reference(args, D):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    threads = os.cpu_count() or 1
+    blocks = 1
+    nblocks = -(-K_DIM // BLOCK)
+    for _ in range(args.warmup):
+        cpu_port_sample(ROWS, D, threads, blocks)
+    full = []
+    for _ in range(args.steps):
+        s, _ = cpu_port_sample(ROWS, D, threads, blocks)
+        full.append(s)
+    sec = sum(full) / len(full)
+    value = ROWS / sec
+    sample = (f"each step: all {ROWS} rows x D={D} projected onto {blocks} of {nblocks} column blocks of "
+              f"{BLOCK} (matrix block generated + matmul), time scaled by {nblocks}/{blocks}")
+    line = {
+        "impl": "reference", "metric": "jl_projected_examples_per_s", "value": value, "unit": "examples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(D),
+        "cpu_baseline": {"value": value, "unit": "examples/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "examples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(D):
+    return {"workload": f"C2 gaussian JL projection: fp16 N(0,1e-2) grads [{ROWS} x {D}] per GPU -> k={K_DIM}, "
+                        f"seed {SEED}, {TILES} feature tiles",
+            "rows_per_gpu": ROWS, "grad_dim": D, "proj_dim": K_DIM, "proj_type": "normal",
+            "l2": "input batch (2.86 GB at full size) is larger than the 126 MB L2; no flush needed"}
+
+
+def run_ours(args, D):
+    import torch
+    import torch.distributed as dist
+    from trak_b200 import _lib, fast_jl
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); "
+                         "use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    g = (torch.randn(ROWS, D, device=dev, generator=gen) * 1e-2).half()
+    out = torch.empty(ROWS, K_DIM, device=dev, dtype=torch.float32)
+
+    def step(timed_events=None):
+        if timed_events is not None:
+            lib.tb_profile_events(timed_events[0].cuda_event, timed_events[1].cuda_event)
+        fast_jl.project(g, K_DIM, SEED, TILES, _lib.TB_NORMAL, out=out, strict=False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _lib.device_status(local)
+
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(args.steps)]
+    for a, b in kev:  # create the underlying CUDA events
+        a.record()
+        b.record()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for i in range(args.steps):
+        step(kev[i])
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    _lib.device_status(local)
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    kernel_ms = torch.tensor([sum(a.elapsed_time(b) for a, b in kev) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(kernel_ms, op=dist.ReduceOp.MAX)
+    ms_total, kernel_ms = ms.item(), kernel_ms.item()
+    value = world * ROWS * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end through the public entry point, host buffers -------------------------
+    e2e_steps = max(1, min(args.steps, 3))
+    host_in = torch.empty(ROWS, D, dtype=torch.float16).pin_memory()
+    host_in.copy_(g)
+    g_stage = torch.empty_like(g)
+    barrier()
+    t_e2e = []
+    for i in range(e2e_steps + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        g_stage.copy_(host_in, non_blocking=True)
+        res = fast_jl.project_normal_32(g_stage, K_DIM, SEED, TILES)
+        res_host = res.cpu()
+        torch.cuda.synchronize()
+        if i > 0:  # first iteration warms the pinned path
+            t_e2e.append(time.perf_counter() - t0)
+    e2e_t = torch.tensor([sum(t_e2e) / len(t_e2e)], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = world * ROWS / e2e_t.item()
+    assert torch.equal(res_host, out.cpu()), "end-to-end result differs from the resident-input result"
+
+    if rank == 0:
+        peak, peak_note = measured_peaks()
+        flop = 2.0 * ROWS * D * K_DIM
+        achieved = flop / (kernel_ms * 1e-3) / 1e12
+        line = {
+            "metric": "jl_projected_examples_per_s", "value": value, "unit": "examples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(D),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_FULL * D / D_FULL,
+                         "kernel": "project_kernel<normal>", "kernel_ms": kernel_ms,
+                         "algorithmic_flop_per_launch": flop, "peak_source": peak_note,
+                         "note": "generator-issue-bound: the Gaussian matrix costs ~550 instructions per "
+                                 "16x32 tile, so the tensor pipe idles; see DESIGN.md"},
+            "e2e": {"value": e2e_value, "unit": "examples/s", "h2d_bytes_per_step": ROWS * D * 2,
+                    "d2h_bytes_per_step": ROWS * K_DIM * 4},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            sec, measured = cpu_port_sample(ROWS, D, threads, 2)
+            nblocks = -(-K_DIM // BLOCK)
+            line["cpu_baseline"] = {
+                "value": ROWS / sec, "unit": "examples/s", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"CPU port of BasicProjector (normal, fp32): all {ROWS} rows x D={D} onto 2 of "
+                          f"{nblocks} column blocks of {BLOCK} in {measured:.1f} s, scaled by {nblocks}/2"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scale", type=float, default=1.0, help="fraction of D (profiler captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    D = max(1024, int(D_FULL * args.scale))
+    if args.impl == "reference":
+        run_reference(args, D)
+    else:
+        run_ours(args, D)
+
+
+if __name__ == "__main__":
+    main()

@@ -86,6 +86,14 @@ int tb_project(int device, void *stream, const void *grads, int dtype, int64_t B
                uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate, void *ws,
                size_t ws_bytes);
 
+/* ---- measurement aid (no counterpart in the reference) -------------------------
+ * Arms the calling thread: the next tb_project call records the two events
+ * (cudaEvent_t passed as void*) on its stream immediately before and after its
+ * projection kernel (of the last 128-row pass), so a benchmark can time that
+ * kernel apart from the restaging and reduction launches around it.  The arming
+ * is consumed by that call; pass NULLs to disarm. */
+int tb_profile_events(void *before, void *after);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,80 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header declares,
+and rejects bad arguments with the documented codes before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from trak_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "trak_b200.h")
+
+
+def _declared():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(tb_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    lib = _lib.lib()
+    names = _declared()
+    assert "tb_project" in names and "tb_version" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/trak_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature in trak_b200/_lib.py"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_error_text():
+    lib = _lib.lib()
+    assert lib.tb_version() >= 100
+    assert lib.tb_strerror(0) == b"ok"
+    assert b"multiple of 512" in lib.tb_strerror(_lib.TB_ERR_BAD_PROJ_DIM)
+    assert lib.tb_strerror(12345) == b"unknown error code"
+
+
+def test_project_workspace_query():
+    lib = _lib.lib()
+    assert lib.tb_project_workspace_bytes(0, 0, 10, 512, 148) == 0
+    small = lib.tb_project_workspace_bytes(0, 8, 1000, 512, 148)
+    big = lib.tb_project_workspace_bytes(0, 128, 11173962, 4096, 148)
+    assert 0 < small < big
+    # staged copy (128 rows x 148 tiles x 75520 padded features x 2 B) + partials
+    assert big >= 128 * 148 * 75520 * 2
+    # more than 128 rows are walked 128 at a time: the workspace does not grow
+    assert lib.tb_project_workspace_bytes(0, 1024, 11173962, 4096, 148) == big
+
+
+def _call(**kw):
+    lib = _lib.lib()
+    a = dict(device=0, stream=None, grads=0x1000, dtype=0, B=8, F=1000, ld=1000, out=0x2000, ld_out=512,
+             N=512, seed=0, tiles=148, ptype=0, alpha=1.0, acc=0, ws=0x10000, ws_bytes=1 << 40)
+    a.update(kw)
+    return lib.tb_project(a["device"], a["stream"], a["grads"], a["dtype"], a["B"], a["F"], a["ld"],
+                          a["out"], a["ld_out"], a["N"], a["seed"], a["tiles"], a["ptype"], a["alpha"],
+                          a["acc"], a["ws"], a["ws_bytes"])
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dtype=7), 1),
+    (dict(B=0), 2), (dict(F=0), 2), (dict(ld=999), 2), (dict(ld_out=100), 2), (dict(tiles=0), 2),
+    (dict(N=500), 3), (dict(N=0), 3), (dict(N=256), 3),
+    (dict(grads=None), 4), (dict(out=None), 4), (dict(ptype=2), 4), (dict(out=0x2004), 4),
+    (dict(ws=None), 5), (dict(ws=0x10010), 5), (dict(ws_bytes=16), 5),
+])
+def test_project_argument_validation(kw, code):
+    # all of these are rejected on the host, before any CUDA call
+    assert _call(**kw) == code
+
+
+def test_check_maps_codes_to_reference_exception_types():
+    with pytest.raises(ValueError, match="multiple of 512"):
+        _lib.check(3)
+    with pytest.raises(RuntimeError):
+        _lib.check(2)
+    with pytest.raises(_lib.DeviceTimeout):
+        _lib.check(7)
+    _lib.check(0)

@@ -1,0 +1,85 @@
+"""Host-side mirror of the reference interface, exercised without a GPU."""
+import pytest
+import torch
+
+from trak_b200 import fast_jl, projectors
+
+
+def test_six_entry_points_exist():
+    for t in ("rademacher", "normal"):
+        for b in (8, 16, 32):
+            assert callable(getattr(fast_jl, f"project_{t}_{b}"))
+
+
+def test_input_checks_match_reference_error_types():
+    # fast_jl.cu:23-27,37 -> RuntimeError; pybind uint32 conversion -> TypeError
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        fast_jl.project_rademacher_8(torch.zeros(8, 100), 512, 0, 148)
+    with pytest.raises(RuntimeError):
+        fast_jl.project_rademacher_8("nope", 512, 0, 148)
+
+
+def test_u32_conversion():
+    assert fast_jl._u32("seed", 5) == 5
+    assert fast_jl._u32("seed", 0xFFFFFFFF) == 0xFFFFFFFF
+    for bad in (-1, 1 << 32, 1.5, "3"):
+        with pytest.raises(TypeError):
+            fast_jl._u32("seed", bad)
+
+
+def test_projection_type_enum():
+    assert projectors.ProjectionType.normal.value == "normal"
+    assert projectors.ProjectionType("rademacher") is projectors.ProjectionType.rademacher
+    assert projectors._ptype_code(projectors.ProjectionType.normal) == 1
+    assert projectors._ptype_code("rademacher") == 0
+    with pytest.raises(KeyError):
+        projectors._ptype_code("gaussian")
+
+
+def test_cuda_projector_rejects_cpu_device():
+    with pytest.raises(ValueError, match="CUDA device"):
+        projectors.CudaProjector(100, 512, 0, projectors.ProjectionType.rademacher, "cpu", 32)
+
+
+def test_vectorize_layout():
+    g = {"w": torch.arange(24.0).reshape(2, 3, 4), "b": torch.tensor([7.0, 8.0]),
+         "v": torch.arange(6.0).reshape(2, 3)}
+    out = projectors.vectorize(g, device="cpu")
+    assert out.shape == (2, 12 + 1 + 3)
+    assert torch.equal(out[0], torch.cat([torch.arange(12.0), torch.tensor([7.0]), torch.arange(3.0)]))
+    assert torch.equal(out[1, 12], torch.tensor(8.0))
+
+
+class _FakeProjector:
+    """Stands in for a per-chunk projector: 'projects' by summing features, scaled by its seed."""
+
+    def __init__(self, seed, proj_dim=4):
+        self.seed, self.proj_dim, self.proj_type = seed, proj_dim, "rademacher"
+        self.calls = []
+
+    def project(self, grads, model_id):
+        self.calls.append(tuple(grads.shape))
+        return grads.float().sum(1, keepdim=True).expand(-1, self.proj_dim) * self.seed
+
+
+def test_chunked_projector_packs_whole_parameters_and_sums_chunks():
+    # three parameters of 6, 1 and 5 features; cap 8 -> chunks [6 + 1, 5]
+    grads = {"a": torch.ones(3, 2, 3), "b": torch.full((3,), 2.0), "c": torch.full((3, 5), 3.0)}
+    fakes = [_FakeProjector(1), _FakeProjector(10)]
+    cp = projectors.ChunkedCudaProjector(fakes, max_chunk_size=8, params_per_chunk=[7, 5], feat_bs=4,
+                                         device=torch.device("cpu"), dtype=torch.float32)
+    out = cp.project(grads, model_id=0)
+    assert out.shape == (3, 4)
+    assert fakes[0].calls == [(3, 7)] and fakes[1].calls == [(3, 5)]
+    assert torch.equal(out, torch.full((3, 4), (6 + 2) * 1.0 + 15 * 10.0))
+    cp.free_memory()
+    assert not cp.input_allocated
+
+
+def test_chunked_projector_detects_inconsistent_chunking():
+    grads = {"a": torch.ones(2, 6), "b": torch.ones(2, 6)}
+    cp = projectors.ChunkedCudaProjector([_FakeProjector(1), _FakeProjector(1)], max_chunk_size=8,
+                                         params_per_chunk=[5, 7], feat_bs=2, device=torch.device("cpu"),
+                                         dtype=torch.float32)
+    with pytest.raises(AssertionError):
+        cp.project(grads, model_id=0)

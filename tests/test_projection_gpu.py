@@ -1,0 +1,268 @@
+"""Parity of the sm_100a projection (called through the C ABI via the fast_jl shim)
+with the CPU oracle, with golden vectors from the reference's compiled kernel, and
+with that kernel itself when its build is present.
+
+Tolerance (floating point): per row, ||out - ref||_2 / ||ref||_2 <= 1e-3 against an
+fp64 host matmul with the identical matrix.  Matrix entries themselves (one-hot
+rows) must be bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import jl_oracle as o
+from oracle import build_ref
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+RAD, NOR = 0, 1
+DT = {"f16": torch.float16, "f32": torch.float32, "bf16": torch.bfloat16}
+
+
+def rel_rows(out, ref):
+    out = np.asarray(out, np.float64)
+    ref = np.asarray(ref, np.float64)
+    num = np.linalg.norm(out - ref, axis=1)
+    den = np.maximum(np.linalg.norm(ref, axis=1), 1e-30)
+    return float((num / den).max())
+
+
+def as_numpy_input(t):
+    return t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
+
+
+def ours(g, N, seed, T, p, **kw):
+    from trak_b200 import fast_jl
+    return fast_jl.project(g, N, seed, T, p, **kw)
+
+
+def one_hot(B, F, feats, dtype, device):
+    g = torch.zeros(B, F, dtype=dtype, device=device)
+    for i, f in enumerate(feats):
+        g[i, f] = 1.0
+    return g
+
+
+SHAPES = [  # B, F, N, seed, tiles
+    (8, 1000, 512, 0, 148),
+    (31, 20000, 1024, 123, 108),
+    (130, 5000, 512, 17, 7),      # more rows than one pass holds
+    (1, 70001, 512, 5, 148),
+    (5, 16, 512, 9, 148),         # fewer features than tiles
+    (3, 1, 512, 2, 1),            # a single feature
+    (16, 4096, 1536, 4, 4),       # tile size a multiple of 64
+]
+
+
+@pytest.mark.parametrize("p", [RAD, NOR])
+@pytest.mark.parametrize("dt", ["f16", "f32", "bf16"])
+@pytest.mark.parametrize("B,F,N,seed,T", SHAPES)
+def test_parity_with_oracle(cuda, p, dt, B, F, N, seed, T):
+    g_cpu = torch.randn(B, F, generator=torch.Generator().manual_seed(B * 1000 + F)).to(DT[dt])
+    out = ours(g_cpu.to(cuda), N, seed, T, p).cpu().numpy()
+    assert out.shape == (B, N) and out.dtype == np.float32
+    if dt == "bf16" and p == NOR:
+        # bf16 gradients meet the fp16-valued matrix rounded once more to bf16
+        P = torch.from_numpy(o.matrix(NOR, F, N, seed, T)).to(torch.bfloat16).double().numpy()
+        ref = g_cpu.double().numpy() @ P
+    else:
+        ref = o.project(p, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
+    assert rel_rows(out, ref) <= TOL
+    if dt == "f32":
+        # still within tolerance of the un-rounded fp32 input (how north-star states it)
+        assert rel_rows(out, o.project(p, g_cpu.numpy(), N, seed, T)) <= TOL
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32", "bf16"])
+@pytest.mark.parametrize("F,N,seed,T", [(1000, 512, 0, 148), (5000, 1024, 123, 108), (70000, 512, 7, 148)])
+def test_rademacher_matrix_rows_bit_exact_vs_oracle(cuda, dt, F, N, seed, T):
+    fts = o.feature_tile_size(F, T)
+    feats = sorted({0, 1, 15, 16, 17, 63, 64, fts - 1, fts, fts + 1, F // 2, F - 1})
+    out = ours(one_hot(len(feats), F, feats, DT[dt], cuda), N, seed, T, RAD).cpu().numpy()
+    assert np.array_equal(out, o.matrix_rows(RAD, F, N, seed, T, feats))
+
+
+def _golden(golden_dir):
+    path = os.path.join(golden_dir, "fastjl_golden.npz")
+    if not os.path.exists(path):
+        pytest.fail("tests/golden/fastjl_golden.npz is missing")
+    return np.load(path)
+
+
+@pytest.mark.parametrize("case", [0, 1, 2, 3])
+@pytest.mark.parametrize("name,p", [("rademacher", RAD), ("normal", NOR)])
+def test_matrix_rows_bit_exact_vs_reference_kernel_golden(cuda, golden_dir, case, name, p):
+    d = _golden(golden_dir)
+    F, N, seed, T = (int(v) for v in d[f"rows_{case}_meta"])
+    feats = d[f"rows_{case}_feats"].tolist()
+    want = d[f"rows_{case}_{name}"].astype(np.float32)
+    for dt in (torch.float16, torch.float32):
+        out = ours(one_hot(8, F, feats, dt, cuda), N, seed, T, p).cpu().numpy()[:len(feats)]
+        assert np.array_equal(out, want), f"{name} rows differ from the reference kernel ({dt})"
+
+
+@pytest.mark.parametrize("case", [0, 1, 2])
+def test_projection_vs_reference_kernel_golden(cuda, golden_dir, case):
+    d = _golden(golden_dir)
+    B, F, N, seed, T, in_seed = (int(v) for v in d[f"proj_{case}_meta"])
+    base = torch.randn(B, F, generator=torch.Generator().manual_seed(in_seed))
+    for dn, dt in (("f16", torch.float16), ("f32", torch.float32)):
+        for name, p in (("rademacher", RAD), ("normal", NOR)):
+            out = ours(base.to(dt).to(cuda), N, seed, T, p).cpu().numpy()
+            assert rel_rows(out, d[f"proj_{case}_{dn}_{name}"]) <= TOL
+
+
+def test_reference_known_answers_even_odd(cuda):
+    # tests/test_rademacher.py:65-108 of the reference
+    for F, parity in ((10240, 0), (10241, 1)):
+        out = ours(torch.ones(8, F, dtype=torch.float16, device=cuda), 1024, 0, 148, RAD).cpu().numpy()
+        assert np.all(np.mod(out, 2) == parity)
+
+
+@pytest.mark.parametrize("F", [1024, 2048])
+@pytest.mark.parametrize("N", [512, 1024, 2048])
+def test_shape_all_entry_points(cuda, F, N):
+    from trak_b200 import fast_jl
+    g = torch.randn(8, F, device=cuda)
+    for t in ("rademacher", "normal"):
+        for b in (8, 16, 32):
+            out = getattr(fast_jl, f"project_{t}_{b}")(g, N, 1, 148)
+            assert out.shape == (8, N) and out.dtype == torch.float32 and out.device == g.device
+
+
+def test_run_to_run_bit_identical(cuda):
+    from trak_b200 import fast_jl
+    g = torch.randn(32, 123457, device=cuda).half()
+    for p in (RAD, NOR):
+        a = ours(g, 2048, 123, 148, p)
+        fast_jl.free_workspaces()
+        b = ours(g, 2048, 123, 148, p)
+        assert torch.equal(a, b)
+        assert torch.equal(a[:7], ours(g[:7].contiguous(), 2048, 123, 148, p))  # rows independent
+
+
+def test_alpha_accumulate_and_strided_rows(cuda):
+    g = torch.randn(12, 3000, device=cuda).half()
+    base = ours(g, 512, 3, 148, RAD)
+    out = torch.full((12, 512), 2.0, device=cuda)
+    ours(g, 512, 3, 148, RAD, alpha=0.5, out=out, accumulate=True)
+    torch.testing.assert_close(out, 2.0 + 0.5 * base, rtol=1e-6, atol=1e-5)
+    wide = torch.randn(12, 5000, device=cuda).half()
+    wide[:, :3000] = g
+    assert torch.equal(ours(wide[:, :3000], 512, 3, 148, RAD, allow_strided=True), base)
+    odd = wide[:, 1:3000]  # rows start on odd (2-byte aligned) addresses
+    assert torch.equal(ours(odd, 512, 3, 148, RAD, allow_strided=True),
+                       ours(odd.contiguous(), 512, 3, 148, RAD))
+
+
+def test_argument_errors_on_device(cuda):
+    from trak_b200 import fast_jl
+    g = torch.randn(8, 1000, device=cuda)
+    with pytest.raises(ValueError, match="multiple of 512"):
+        fast_jl.project_rademacher_8(g, 500, 0, 148)
+    with pytest.raises(RuntimeError):
+        fast_jl.project_rademacher_8(g.long(), 512, 0, 148)
+    with pytest.raises(RuntimeError):
+        fast_jl.project_rademacher_8(g.t(), 512, 0, 148)
+    with pytest.raises(RuntimeError):
+        fast_jl.project_rademacher_8(g[0], 512, 0, 148)
+    with pytest.raises(TypeError):
+        fast_jl.project_rademacher_8(g, 512, -1, 148)
+
+
+def test_norm_and_inner_product_preservation(cuda):
+    # statistical JL property (tests/test_jl.py:159-282 of the reference), at 1/sqrt(k) scale
+    k = 4096
+    g = torch.randn(16, 200000, device=cuda)
+    for p in (RAD, NOR):
+        y = ours(g, k, 11, 148, p).double() / k ** 0.5
+        gd = g.double()
+        ratio = (y.norm(dim=1) / gd.norm(dim=1)).cpu().numpy()
+        assert np.all(np.abs(ratio - 1) < 0.1)
+        ip = (y @ y.T - gd @ gd.T).abs().max().item() / (gd.norm(dim=1).max().item() ** 2)
+        assert ip < 0.1
+
+
+def test_projector_classes(cuda):
+    from trak_b200 import projectors as pj
+    torch.manual_seed(0)
+    grads = {"w1": torch.randn(6, 40, 50, device=cuda), "b1": torch.randn(6, device=cuda),
+             "w2": torch.randn(6, 3000, device=cuda)}
+    D = 2000 + 1 + 3000
+    proj = pj.CudaProjector(D, 1024, 5, pj.ProjectionType.rademacher, cuda, 32)
+    flat = pj.vectorize(grads, device=cuda)
+    a = proj.project(grads, model_id=2)
+    ref = o.project(RAD, flat.cpu().numpy(), 1024, 5 + 20000, proj.num_sms, round_f16=True)
+    assert rel_rows(a.cpu().numpy(), ref) <= TOL
+    # chunked: [w1, b1] and [w2] with their own seeds, summed
+    p0 = pj.CudaProjector(2001, 1024, 7, pj.ProjectionType.rademacher, cuda, 32)
+    p1 = pj.CudaProjector(3000, 1024, 9, pj.ProjectionType.rademacher, cuda, 32)
+    cp = pj.ChunkedCudaProjector([p0, p1], 3500, [2001, 3000], 8, cuda, torch.float32)
+    got = cp.project(grads, model_id=0)
+    want = p0.project(flat[:, :2001].contiguous(), 0) + p1.project(flat[:, 2001:].contiguous(), 0)
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-3)
+    assert got.shape == (6, 1024)
+
+
+def test_full_size_properties(cuda):
+    """The benchmark's shape (128 x 11,173,962 fp16 -> 4096, 148 tiles): matrix rows at the far end
+    of the feature range against the oracle, linearity and run-to-run identity."""
+    B, F, N, seed, T = 128, 11_173_962, 4096, 17, 148
+    fts = o.feature_tile_size(F, T)
+    assert fts == 75500
+    feats = [0, fts - 1, fts * 147, F - 1]
+    g = torch.zeros(B, F, dtype=torch.float16, device=cuda)
+    for i, f in enumerate(feats):
+        g[i, f] = 1.0
+    g[4:] = (torch.randn(B - 4, F, device=cuda) * 1e-2).half()
+    rad = ours(g, N, seed, T, RAD)
+    assert np.array_equal(rad[:4].cpu().numpy(), o.matrix_rows(RAD, F, N, seed, T, feats))
+    nor = ours(g, N, seed, T, NOR)
+    want = o.matrix_rows(NOR, F, N, seed, T, feats[:2] + feats[3:])
+    got = nor[[0, 1, 3]].cpu().numpy()
+    # host libm vs device logf / __sincosf (absolute error ~1e-6 before the fp16 rounding):
+    # equal except for a last-place difference on a small fraction of entries
+    assert (got != want).mean() < 0.01
+    np.testing.assert_allclose(got, want, rtol=2 ** -10, atol=4e-6)
+    assert torch.equal(nor, ours(g, N, seed, T, NOR))
+    # linearity on exactly representable combinations: P(a) + P(b) == P(a + b) for one-hot a, b
+    s = torch.zeros(8, F, dtype=torch.float16, device=cuda)
+    s[0, feats[0]] = 1.0
+    s[0, feats[3]] = 1.0
+    both = ours(s, N, seed, T, RAD)[0]
+    assert torch.equal(both, rad[0] + rad[3])
+    # norms: E||Pg||^2 = k ||g||^2
+    ratio = (rad[4:].double().norm(dim=1) / (g[4:].double().norm(dim=1) * N ** 0.5)).cpu().numpy()
+    assert np.all(np.abs(ratio - 1) < 0.05)
+
+
+# ---- against the compiled reference kernel itself, when it travelled with the repo ----
+
+def _witness():
+    w = build_ref.load()
+    if w is None:
+        pytest.skip("oracle/_ref/fast_jl.so not built (run oracle/build_ref.py where the reference is)")
+    return w
+
+
+@pytest.mark.parametrize("B,F,N,seed,T", [(8, 1000, 512, 0, 148), (32, 100000, 4096, 123, 108),
+                                          (16, 33333, 1024, 5, 148)])
+def test_bit_exact_matrix_and_parity_vs_reference_kernel(cuda, B, F, N, seed, T):
+    w = _witness()
+    fts = o.feature_tile_size(F, T)
+    feats = [0, 1, 15, 16, fts - 1, fts, F // 2, F - 1][:B]
+    for dt in (torch.float16, torch.float32):
+        g1 = one_hot(B, F, feats, dt, cuda)
+        g = torch.randn(B, F, device=cuda).to(dt)
+        for name, p in (("rademacher", RAD), ("normal", NOR)):
+            ref_fn = getattr(w, f"project_{name}_32")
+            assert torch.equal(ours(g1, N, seed, T, p), ref_fn(g1, N, seed, T))
+            assert rel_rows(ours(g, N, seed, T, p).cpu().numpy(), ref_fn(g, N, seed, T).cpu().numpy()) <= TOL
+
+
+def test_device_status_clean(cuda):
+    from trak_b200 import _lib
+    _lib.device_status(cuda.index)

@@ -16,6 +16,14 @@ void set_cuda_error(const char* what, const char* file, int line) {
     snprintf(t_cuda_error, sizeof(t_cuda_error), "%s (%s:%d)", what, file, line);
 }
 
+static thread_local cudaEvent_t t_ev_before = nullptr, t_ev_after = nullptr;
+
+void take_profile_events(cudaEvent_t* before, cudaEvent_t* after) {
+    *before = t_ev_before;
+    *after = t_ev_after;
+    t_ev_before = t_ev_after = nullptr;
+}
+
 static std::mutex g_mu;
 static constexpr int MAX_DEV = 64;
 static int g_dev_state[MAX_DEV];  // 0 unknown, 1 ok, -1 unsupported
@@ -111,6 +119,12 @@ const char* tb_strerror(int code) {
 }
 
 const char* tb_last_cuda_error(void) { return tb::t_cuda_error; }
+
+int tb_profile_events(void* before, void* after) {
+    tb::t_ev_before = static_cast<cudaEvent_t>(before);
+    tb::t_ev_after = static_cast<cudaEvent_t>(after);
+    return TB_OK;
+}
 
 int tb_device_status(int device, uint32_t* detail) {
     int rc = tb::select_device(device, nullptr);

@@ -33,6 +33,9 @@ uint32_t* status_ptr(int device);
 int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
 
+// Events armed by tb_profile_events for this thread (null when not armed); taking clears them.
+void take_profile_events(cudaEvent_t* before, cudaEvent_t* after);
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace tb
