@@ -36,6 +36,7 @@ extern "C" {
 #define TB_ERR_CUDA 6           /* a CUDA runtime / driver call failed (see tb_last_cuda_error) */
 #define TB_ERR_DEVICE_TIMEOUT 7 /* a bounded wait inside a kernel ran out                 */
 #define TB_ERR_UNSUPPORTED 8    /* not a B200-class device, or size beyond a stated limit */
+#define TB_ERR_SCRATCH_LIMIT 9  /* tb_project_static: the shape needs more than the built-in scratch */
 
 #define TB_F16 0
 #define TB_BF16 1
@@ -85,6 +86,29 @@ int tb_project(int device, void *stream, const void *grads, int dtype, int64_t B
                int64_t ld, float *out, int64_t ld_out, uint32_t N, uint32_t seed,
                uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate, void *ws,
                size_t ws_bytes);
+
+/* ---- projection without a caller-provided workspace ------------------------------
+ * No counterpart in the reference.  Same arguments and result as tb_project, minus
+ * `ws` / `ws_bytes`: the scratch lives in a fixed array inside the loaded library
+ * (TB_PROJECT_STATIC_SCRATCH_BYTES on every GPU that loads it, held until the
+ * process exits).  Meant for hosts that cannot allocate device memory themselves,
+ * e.g. a plugin in a process whose device memory already belongs to another
+ * component's pool, or a serving loop that must avoid the device-wide
+ * synchronisation of cudaMalloc / cudaFree.  The call allocates nothing.
+ *
+ *   - shapes with tb_project_workspace_bytes(...) > TB_PROJECT_STATIC_SCRATCH_BYTES
+ *     are refused with TB_ERR_SCRATCH_LIMIT
+ *   - the first call on a device looks up the array's device address (a one-time
+ *     set-up per device); make that first call before starting any stream capture
+ *   - all calls on a device share the one array: calls whose kernels may overlap on
+ *     the GPU (different streams, different threads) race on it and must be
+ *     serialised by the caller.  The array keeps the previous call's bytes; every
+ *     byte a call reads it has written first, so no clearing is needed. */
+#define TB_PROJECT_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+int tb_project_static(int device, void *stream, const void *grads, int dtype, int64_t B, int64_t F,
+                      int64_t ld, float *out, int64_t ld_out, uint32_t N, uint32_t seed,
+                      uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate);
 
 /* ---- measurement aid (no counterpart in the reference) -------------------------
  * Arms the calling thread: the next tb_project call records the two events

@@ -30,6 +30,7 @@ SIGNATURES = {
     "tb_device_status": (_i, [_i, ctypes.POINTER(_u32)]),
     "tb_project_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32]),
     "tb_profile_events": (_i, [_vp, _vp]),
+    "tb_project_static": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i]),
     "tb_project": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i,
                         _vp, _sz]),
 }

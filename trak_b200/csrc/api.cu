@@ -114,6 +114,8 @@ const char* tb_strerror(int code) {
     case TB_ERR_CUDA: return "CUDA error";
     case TB_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
     case TB_ERR_UNSUPPORTED: return "unsupported device or size";
+    case TB_ERR_SCRATCH_LIMIT:
+        return "shape needs more scratch than tb_project_static's built-in array; use tb_project with a workspace";
     default: return "unknown error code";
     }
 }
