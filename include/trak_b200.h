@@ -37,6 +37,7 @@ extern "C" {
 #define TB_ERR_DEVICE_TIMEOUT 7 /* a bounded wait inside a kernel ran out                 */
 #define TB_ERR_UNSUPPORTED 8    /* not a B200-class device, or size beyond a stated limit */
 #define TB_ERR_SCRATCH_LIMIT 9  /* tb_project_static: the shape needs more than the built-in scratch */
+#define TB_ERR_NOT_SPD 10       /* tb_spd_inverse met a non-positive pivot (reported by tb_device_status) */
 
 #define TB_F16 0
 #define TB_BF16 1
@@ -52,8 +53,9 @@ const char *tb_strerror(int code);
 const char *tb_last_cuda_error(void);
 
 /* Synchronises `device` and returns TB_OK, or TB_ERR_DEVICE_TIMEOUT if any
- * kernel of this library gave up a wait since the last call (the word is
- * cleared by the call).  *detail, if not null, receives the raw status word. */
+ * kernel of this library gave up a wait since the last call, or TB_ERR_NOT_SPD if
+ * tb_spd_inverse met a non-positive pivot (the word is cleared by the call).
+ * *detail, if not null, receives the raw status word. */
 int tb_device_status(int device, uint32_t *detail);
 
 /* ---- JL projection ---------------------------------------------------------
@@ -86,6 +88,42 @@ int tb_project(int device, void *stream, const void *grads, int dtype, int64_t B
                int64_t ld, float *out, int64_t ld_out, uint32_t N, uint32_t seed,
                uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate, void *ws,
                size_t ws_bytes);
+
+/* ---- after-kernel scoring -------------------------------------------------------
+ * The three products and the inverse of the reference's BasicScoreComputer
+ * (trak/score_computers.py:114-189).  Matrices are row-major; `dtype` is the type of
+ * the inputs (TB_F16 / TB_BF16 / TB_F32), results are fp32.  fp32 inputs are split
+ * into bf16 hi + lo planes and multiplied with three tensor-core passes (about 1e-5
+ * relative error); 16-bit inputs are used as they are.  Workspaces: 256-byte aligned,
+ * at least the size the matching *_workspace_bytes query returns.
+ *
+ * tb_gram        G[k x k] (+)= X^T X for X [n x k]            get_xtx, :145-155
+ *                (full symmetric G; call it per row block with accumulate = 1)
+ * tb_spd_inverse A <- inv(A + lambda I) in place, fp32, through Cholesky; with
+ *                rescale_by_mean_abs the result is divided by its mean absolute
+ *                entry as in :160-168 (torch.linalg.inv + `/= abs().mean()` there).
+ *                mean_abs_out (device pointer, nullable) receives that mean.  A
+ *                matrix that is not positive definite is reported by
+ *                tb_device_status as TB_ERR_NOT_SPD.
+ * tb_gemm_nt     C[M x N] (+)= alpha * row_scale[m] * A[M x K] . B[N x K]^T
+ *                get_x_xtx_inv's `block @ xtx_inv` (:170-176; the inverse is symmetric,
+ *                so it is its own transpose) and get_scores' `features @ target_grads.T`
+ *                (:187-189, trak/utils.py:128-133).  row_scale (device pointer,
+ *                nullable, length M) fuses the out-to-loss weighting that the
+ *                reference applies on the host afterwards (trak/traker.py:676-678).
+ */
+size_t tb_gram_workspace_bytes(int dtype, int64_t n, int64_t k);
+int tb_gram(int device, void *stream, const void *X, int dtype, int64_t n, int64_t k, int64_t ld,
+            float *G, int64_t ldg, int accumulate, void *ws, size_t ws_bytes);
+
+size_t tb_spd_inverse_workspace_bytes(int64_t k);
+int tb_spd_inverse(int device, void *stream, float *A, int64_t k, int64_t lda, float lambda,
+                   int rescale_by_mean_abs, float *mean_abs_out, void *ws, size_t ws_bytes);
+
+size_t tb_gemm_nt_workspace_bytes(int dtype, int64_t M, int64_t N, int64_t K);
+int tb_gemm_nt(int device, void *stream, const void *A, int64_t lda, const void *B, int64_t ldb,
+               int dtype, int64_t M, int64_t N, int64_t K, float *C, int64_t ldc,
+               const float *row_scale, float alpha, int accumulate, void *ws, size_t ws_bytes);
 
 /* ---- projection without a caller-provided workspace ------------------------------
  * No counterpart in the reference.  Same arguments and result as tb_project, minus

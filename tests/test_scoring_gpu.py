@@ -1,0 +1,127 @@
+"""Parity of the sm_100a scoring path (through the C ABI) with the reference's CPU
+BasicScoreComputer: against fixtures produced by the unmodified reference and against
+its CPU port on seeded inputs.
+
+Tolerance: Frobenius-relative 1e-3 for Gram, features and scores (what north-star
+states for the scores); the fp32 bf16-split GEMMs land around 1e-5.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import basic_ref as br
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def rel(a, b):
+    a = torch.as_tensor(a).double().cpu()
+    b = torch.as_tensor(b).double().cpu()
+    return float((a - b).norm() / b.norm())
+
+
+def test_pipeline_matches_reference_fixture(cuda, golden_dir):
+    from trak_b200.score_computers import B200ScoreComputer
+    d = np.load(os.path.join(golden_dir, "basic_scoring.npz"))
+    n, k, m, lam = int(d["n"]), int(d["k"]), int(d["m"]), float(d["lam"])
+    X = torch.randn(n, k, generator=torch.Generator().manual_seed(int(d["x_seed"]))) / k ** 0.5
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(int(d["t_seed"]))) / k ** 0.5
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, CUDA_MAX_DIM_SIZE=int(d["block_rows"]), lambda_reg=lam)
+    gram = sc.get_xtx(X)                      # CPU input, like TRAKer's memmaps
+    feats = sc.get_x_xtx_inv(X, gram)
+    acc = torch.zeros(n, m)                   # CPU accumulator, as in trak/traker.py:632
+    sc.get_scores(feats, T, acc)
+    assert gram.shape == (k, k) and feats.shape == (n, k) and gram.dtype == torch.float32
+    assert rel(gram, d["gram"]) <= TOL
+    assert rel(feats, d["features"]) <= TOL
+    assert rel(acc, d["scores"]) <= TOL
+    sc.get_scores(feats, T, acc)              # accumulates
+    assert rel(acc, 2 * d["scores"]) <= TOL
+
+
+@pytest.mark.parametrize("n,k,m,lam,dtype", [
+    (3000, 256, 100, 1e-3, torch.float32),
+    (2500, 333, 77, 1e-2, torch.float32),      # nothing a multiple of the tile sizes
+    (4000, 512, 1000, 1e-3, torch.float16),    # TRAKer's default storage dtype
+    (300, 64, 5, 0.5, torch.float32),
+])
+def test_pipeline_matches_cpu_port(cuda, n, k, m, lam, dtype):
+    from trak_b200.score_computers import B200ScoreComputer
+    X = (torch.randn(n, k, generator=torch.Generator().manual_seed(n)) / k ** 0.5).to(dtype)
+    T = (torch.randn(m, k, generator=torch.Generator().manual_seed(m)) / k ** 0.5).to(dtype)
+    sc = B200ScoreComputer(dtype=dtype, device=cuda, CUDA_MAX_DIM_SIZE=1024, lambda_reg=lam)
+    gram = sc.get_xtx(X.to(cuda))
+    feats = sc.get_x_xtx_inv(X.to(cuda), gram)
+    acc = torch.zeros(n, m)
+    sc.get_scores(feats, T.to(cuda), acc)
+    assert gram.dtype == dtype and feats.dtype == dtype
+    Xf, Tf = X.float(), T.float()
+    g_ref = br.xtx(Xf)
+    f_ref = br.x_xtx_inv(Xf, g_ref, lam)
+    s_ref = torch.zeros(n, m)
+    br.scores(f_ref, Tf, s_ref)
+    tol = TOL if dtype == torch.float32 else 3e-3   # fp16 storage of the Gram and the features
+    assert rel(gram, g_ref) <= tol
+    assert rel(feats, f_ref) <= tol
+    assert rel(acc, s_ref) <= tol
+
+
+def test_primitives_against_fp64(cuda):
+    from trak_b200 import score_computers as sc
+    torch.manual_seed(0)
+    a = torch.randn(257, 70, device=cuda)
+    b = torch.randn(513, 70, device=cuda)
+    assert rel(sc.gemm_nt(a, b), a.double() @ b.double().T) <= 1e-4
+    w = torch.rand(257, device=cuda)
+    out = torch.ones(257, 513, device=cuda)
+    sc.gemm_nt(a, b, out=out, row_scale=w, alpha=0.5, accumulate=True)
+    assert rel(out, 1.0 + 0.5 * w.double()[:, None] * (a.double() @ b.double().T)) <= 1e-4
+    x = torch.randn(1000, 130, device=cuda)
+    g = sc.gram(x)
+    assert torch.equal(g, g.T)                # stored twice from the same accumulator
+    assert rel(g, x.double().T @ x.double()) <= 1e-4
+    for k in (1, 63, 64, 65, 200):
+        y = torch.randn(4 * k + 3, k, device=cuda, dtype=torch.float64)
+        A = (y.T @ y / k).float()
+        inv = sc.spd_inverse_(A.clone(), 1e-2, rescale=False)
+        ref = torch.linalg.inv(A.double() + 1e-2 * torch.eye(k, device=cuda, dtype=torch.float64))
+        assert rel(inv, ref) <= 1e-4
+        inv2 = sc.spd_inverse_(A.clone(), 1e-2, rescale=True)
+        assert rel(inv2, ref / ref.abs().mean()) <= 1e-4
+
+
+def test_fused_out_to_loss_weighting(cuda):
+    # the host epilogue of trak/traker.py:676-678 with one checkpoint, fused as a row scale
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m = 900, 128, 40
+    F = torch.randn(n, k, generator=torch.Generator().manual_seed(1))
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(2))
+    w = torch.rand(n, 1, generator=torch.Generator().manual_seed(3))
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, CUDA_MAX_DIM_SIZE=400)
+    acc = torch.zeros(n, m)
+    sc.get_scores(F, T, acc, row_scale=w)
+    plain = torch.zeros(n, m)
+    br.scores(F, T, plain)
+    assert rel(acc, br.finalize_scores_epilogue(plain, w, 1)) <= TOL
+
+
+def test_not_positive_definite_is_reported(cuda):
+    from trak_b200 import _lib, score_computers as sc
+    with pytest.raises(_lib.NotPositiveDefinite):
+        sc.spd_inverse_(-torch.eye(100, device=cuda), 0.0)
+    _lib.device_status(cuda.index)            # the status word was cleared
+
+
+def test_larger_shape_properties(cuda):
+    # k = 2048: symmetry, inverse times matrix = identity, agreement with an fp64 solve
+    from trak_b200 import score_computers as sc
+    k, n = 2048, 16384
+    x = torch.randn(n, k, device=cuda) / k ** 0.5
+    g = sc.gram(x)
+    assert torch.equal(g, g.T)
+    inv = sc.spd_inverse_(g.clone(), 1e-3, rescale=False)
+    eye = (g.double() + 1e-3 * torch.eye(k, device=cuda, dtype=torch.float64)) @ inv.double()
+    assert float((eye - torch.eye(k, device=cuda, dtype=torch.float64)).abs().max()) < 1e-3

@@ -15,6 +15,7 @@ TB_RADEMACHER, TB_NORMAL = 0, 1
 TB_OK = 0
 TB_ERR_BAD_PROJ_DIM = 3
 TB_ERR_DEVICE_TIMEOUT = 7
+TB_ERR_NOT_SPD = 10
 
 _lib = None
 _lock = threading.Lock()
@@ -30,6 +31,12 @@ SIGNATURES = {
     "tb_device_status": (_i, [_i, ctypes.POINTER(_u32)]),
     "tb_project_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32]),
     "tb_profile_events": (_i, [_vp, _vp]),
+    "tb_gram_workspace_bytes": (_sz, [_i, _i64, _i64]),
+    "tb_gram": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _i, _vp, _sz]),
+    "tb_spd_inverse_workspace_bytes": (_sz, [_i64]),
+    "tb_spd_inverse": (_i, [_i, _vp, _vp, _i64, _i64, _f, _i, _vp, _vp, _sz]),
+    "tb_gemm_nt_workspace_bytes": (_sz, [_i, _i64, _i64, _i64]),
+    "tb_gemm_nt": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i, _i64, _i64, _i64, _vp, _i64, _vp, _f, _i, _vp, _sz]),
     "tb_project_static": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i]),
     "tb_project": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i,
                         _vp, _sz]),
@@ -58,6 +65,11 @@ class DeviceTimeout(RuntimeError):
     pass
 
 
+class NotPositiveDefinite(RuntimeError):
+    """tb_spd_inverse met a non-positive Cholesky pivot (torch.linalg.inv of the reference would
+    return garbage or raise on such a matrix)."""
+
+
 def check(rc: int) -> None:
     """Maps a status code to the exception type the reference raises for it:
     ValueError for a bad projection dimension (std::invalid_argument in
@@ -72,6 +84,8 @@ def check(rc: int) -> None:
         msg = f"CUDA error: {l.tb_last_cuda_error().decode()}"
     if rc == TB_ERR_DEVICE_TIMEOUT:
         raise DeviceTimeout(msg)
+    if rc == TB_ERR_NOT_SPD:
+        raise NotPositiveDefinite(msg)
     raise RuntimeError(f"trak_b200: {msg} (code {rc})")
 
 

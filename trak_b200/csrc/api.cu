@@ -62,7 +62,8 @@ typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
 static encode_fn g_encode = nullptr;
 
 int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
-                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                CUtensorMapSwizzle swizzle) {
     {
         std::lock_guard<std::mutex> lk(g_mu);
         if (!g_encode) {
@@ -86,7 +87,7 @@ int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const v
         if (i + 1 < rank) gstr[i] = strides_bytes[i];
     }
     CUresult r = g_encode(map, dt, rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         char msg[96];
@@ -114,6 +115,7 @@ const char* tb_strerror(int code) {
     case TB_ERR_CUDA: return "CUDA error";
     case TB_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
     case TB_ERR_UNSUPPORTED: return "unsupported device or size";
+    case TB_ERR_NOT_SPD: return "matrix is not positive definite (non-positive Cholesky pivot)";
     case TB_ERR_SCRATCH_LIMIT:
         return "shape needs more scratch than tb_project_static's built-in array; use tb_project with a workspace";
     default: return "unknown error code";
@@ -137,7 +139,7 @@ int tb_device_status(int device, uint32_t* detail) {
     if (detail) *detail = host[0];
     if (host[0] != 0) {
         TB_CUDA(cudaMemset(tb::status_ptr(device), 0, sizeof(host)));
-        return TB_ERR_DEVICE_TIMEOUT;
+        return host[0] == 6u ? TB_ERR_NOT_SPD : TB_ERR_DEVICE_TIMEOUT;
     }
     return TB_OK;
 }

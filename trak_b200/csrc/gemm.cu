@@ -1,0 +1,435 @@
+// Tensor-core GEMM for the after-kernel scoring:  C[M x N] (+)= alpha * s[m] * A[M x K] . B[N x K]^T
+//
+// Used for the three products of the reference's BasicScoreComputer
+// (trak/score_computers.py:145-189):  X^T X  (A = B = X^T, symmetric mode),
+// X . inv  (inv is symmetric, so it is its own transpose) and  features . targets^T.
+//
+// fp32 inputs are not rounded to one tensor-core format.  A packing pass splits every
+// value into bf16 hi + bf16 lo (hi = rn(x), lo = rn(x - hi); together 16 mantissa bits)
+// and the kernel accumulates  hi*hi + hi*lo + lo*hi  in fp32 -- three MMAs per k-step at
+// the bf16 rate, about 1e-5 relative error where one TF32 pass gives about 5e-4.  fp16 and
+// bf16 inputs are exact in one plane and take one MMA per k-step.
+//
+// The packing pass also tiles the operands the way the pipeline consumes them:
+// [128-row block][32-wide k block][plane][128 rows][32 k], so every TMA box is one
+// contiguous 8 KB run, and it can transpose (for X^T X the operand is X^T).
+//
+// Kernel: one CTA per 256 x 256 tile of C.  Warp 0 issues TMA (64-byte swizzle boxes,
+// never multicast), warp 1 issues tcgen05.mma (both operands from shared memory,
+// M = 128, N = 256, two accumulators fill the 512 TMEM columns), warps 4-11 run the
+// epilogue (tcgen05.ld, scale, optional accumulate, optional mirrored store for the
+// symmetric product).  Every mbarrier wait is bounded.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm.h"
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace tb {
+
+constexpr uint32_t GK = 32;                 // k per pipeline stage (one 64-byte swizzle row)
+constexpr uint32_t GTILE_BYTES = 128 * GK * 2;  // one [128 x 32] 16-bit tile: 8 KB
+
+struct GemmParams {
+    float* C;
+    const float* row_scale;  // nullable, length M
+    uint32_t* status;
+    int64_t ldc;
+    uint32_t M, N;
+    uint32_t kblocks;        // K / 32 (padded)
+    uint32_t stages;
+    uint32_t idesc;
+    float alpha;
+    int accumulate;
+    int symmetric;           // A and B are the same packed operand; only tiles on/above the
+                             // diagonal are computed and every result is stored twice
+};
+
+// K-major tile, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) |
+           (4ull << 61);
+}
+
+__device__ __forceinline__ void gemm_fail(uint32_t* status, volatile uint32_t* abort_flag, uint32_t code,
+                                          uint32_t detail) {
+    *abort_flag = 1u;
+    if (atomicCAS(status, 0u, code) == 0u) {
+        status[1] = blockIdx.x + gridDim.x * blockIdx.y;
+        status[2] = detail;
+    }
+}
+
+template <int NPL>
+__global__ void __launch_bounds__(384, 1)
+gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+    constexpr uint32_t MAXS = 8;
+    constexpr uint32_t A_BYTES = 2 * NPL * GTILE_BYTES;  // two row blocks x planes
+    constexpr uint32_t STAGE_BYTES = 2 * A_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[MAXS];
+    __shared__ uint64_t bar_empty[MAXS];
+    __shared__ uint64_t bar_acc;
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_word;
+    volatile uint32_t* abort_flag = &abort_word;
+
+    const uint32_t tile_m = blockIdx.y, tile_n = blockIdx.x;
+    if (p.symmetric && tile_n < tile_m) return;  // whole CTA leaves before any barrier or TMEM use
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t S = p.stages;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        abort_word = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        prefetch_tmap(&map_a);
+        prefetch_tmap(&map_b);
+        uint32_t slot = 0, ph = 0;
+        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) {
+                gemm_fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, kb);
+                break;
+            }
+            const uint32_t bar = smem_u32(&bar_full[slot]);
+            const uint32_t sa = smem_base + slot * STAGE_BYTES, sb = sa + A_BYTES;
+            mbar_expect_tx(bar, STAGE_BYTES);
+            // packed row index of (row block rb, k block kb, plane pl): ((rb*kblocks + kb)*NPL + pl)*128
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t rb_a = tile_m * 2u + h, rb_b = tile_n * 2u + h;
+#pragma unroll
+                for (uint32_t pl = 0; pl < (uint32_t)NPL; ++pl) {
+                    // A: [block h][plane]; B: [plane][block h] so that 256 rows of one plane are adjacent
+                    tma_load_2d(sa + (h * NPL + pl) * GTILE_BYTES, &map_a, 0,
+                                (int)(((rb_a * p.kblocks + kb) * NPL + pl) * 128u), bar);
+                    tma_load_2d(sb + (pl * 2u + h) * GTILE_BYTES, &map_b, 0,
+                                (int)(((rb_b * p.kblocks + kb) * NPL + pl) * 128u), bar);
+                }
+            }
+            if (++slot == S) {
+                slot = 0;
+                ph ^= 1u;
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // -------------------------------- MMA issuer --------------------------------
+        uint32_t slot = 0, ph = 0;
+        bool ok = true;
+        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_full[slot]), ph, abort_flag)) {
+                gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, kb);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t sa = smem_base + slot * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+            for (uint32_t mb = 0; mb < 2; ++mb) {
+                const uint32_t d = tmem_base + mb * 256u;
+#pragma unroll
+                for (uint32_t kk = 0; kk < 2; ++kk) {
+                    const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                    const uint64_t a_hi = smem_desc_k_sw64(sa + (mb * NPL) * GTILE_BYTES) + 2u * kk;
+                    const uint64_t b_hi = smem_desc_k_sw64(sb) + 2u * kk;
+                    umma_f16_ss(d, a_hi, b_hi, p.idesc, acc);
+                    if (NPL == 2) {
+                        const uint64_t a_lo = smem_desc_k_sw64(sa + (mb * NPL + 1) * GTILE_BYTES) + 2u * kk;
+                        const uint64_t b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES) + 2u * kk;
+                        umma_f16_ss(d, a_hi, b_lo, p.idesc, 1u);
+                        umma_f16_ss(d, a_lo, b_hi, p.idesc, 1u);
+                    }
+                }
+            }
+            tc_commit(smem_u32(&bar_empty[slot]));
+            if (++slot == S) {
+                slot = 0;
+                ph ^= 1u;
+            }
+        }
+        if (ok) tc_commit(smem_u32(&bar_acc));
+    } else if (warp >= 4) {
+        // --------------------------------- epilogue ---------------------------------
+        const uint32_t q = warp & 3u, chalf = (warp - 4u) >> 2;  // TMEM lane quarter, column half
+        bool got = mbar_wait(smem_u32(&bar_acc), 0u, abort_flag);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) {
+            if (lane == 0) gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, warp);
+        } else {
+            tc_fence_after();
+            const uint32_t lane_base = (q * 32u) << 16;
+            // symmetric product: every pair (m, n), n >= m, is taken from one accumulator entry and
+            // stored at C[m, n] and C[n, m], so the result is exactly symmetric
+            const bool sym = p.symmetric != 0;
+#pragma unroll 1
+            for (uint32_t mb = 0; mb < 2; ++mb) {
+                const uint32_t m = tile_m * 256u + mb * 128u + q * 32u + lane;
+                const float rs = p.alpha * ((p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f);
+#pragma unroll 1
+                for (uint32_t cb = 0; cb < 8; ++cb) {
+                    const uint32_t c0 = chalf * 128u + cb * 16u;
+                    uint32_t r[16];
+                    tmem_ld_x16(tmem_base + lane_base + mb * 256u + c0, r);
+                    tmem_wait_ld();
+                    const uint32_t n0 = tile_n * 256u + c0;
+                    if (m < p.M) {
+                        float* dst = p.C + (int64_t)m * p.ldc + n0;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (n0 + j < p.N && (!sym || n0 + j >= m)) {
+                                float v = rs * __uint_as_float(r[j]);
+                                if (p.accumulate) v += dst[j];
+                                dst[j] = v;
+                            }
+                        }
+                    }
+                    if (sym && m < p.N) {
+                        // C[n, m]: for a fixed j the warp's lanes hold consecutive m -> coalesced
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (n0 + j < p.M && n0 + j > m) {
+                                float* dst = p.C + (int64_t)(n0 + j) * p.ldc + m;
+                                float v = p.alpha * __uint_as_float(r[j]);
+                                if (p.accumulate) v += *dst;
+                                *dst = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) __nanosleep(200000);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- packing ---------------------------------------------------------------------------
+// packed[((rb*kblocks + kb)*NPL + pl)*128 + r][kk]  (16-bit), r < 128, kk < 32:
+//   operand row  R = rb*128 + r,  k = kb*32 + kk;
+//   value = src[R*ld + k]  (TRANS = false)  or  src[k*ld + R]  (TRANS = true: the operand is the
+//   transpose of the row-major source), zero outside [rows x K].
+// In: float (NPL = 2: bf16 hi / lo planes) or a 16-bit type copied as is (NPL = 1).
+template <typename In, int NPL, bool TRANS>
+__global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ packed, uint64_t rows,
+                            uint64_t K, uint64_t ld, uint32_t rowblocks, uint32_t kblocks) {
+    // one thread = 8 consecutive k of one operand row (a 16-byte store per plane)
+    const uint64_t total = (uint64_t)rowblocks * kblocks * 128u * 4u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        uint32_t r, oct;
+        uint64_t rest;
+        if (TRANS) {  // lanes run along operand rows = consecutive source columns
+            r = (uint32_t)(i & 127u);
+            oct = (uint32_t)((i >> 7) & 3u);
+        } else {      // lanes run along k = consecutive source columns
+            oct = (uint32_t)(i & 3u);
+            r = (uint32_t)((i >> 2) & 127u);
+        }
+        rest = i >> 9;
+        const uint32_t kb = (uint32_t)(rest % kblocks);
+        const uint64_t rb = rest / kblocks;
+        const uint64_t R = rb * 128u + r, k0 = (uint64_t)kb * 32u + oct * 8u;
+        uint16_t hi[8], lo[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            hi[e] = 0;
+            lo[e] = 0;
+            if (R < rows && k0 + e < K) {
+                const In x = TRANS ? src[(k0 + e) * ld + R] : src[R * ld + k0 + e];
+                if constexpr (sizeof(In) == 4) {
+                    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+                    const __nv_bfloat16 l = __float2bfloat16_rn(x - __bfloat162float(h));
+                    hi[e] = *reinterpret_cast<const uint16_t*>(&h);
+                    lo[e] = *reinterpret_cast<const uint16_t*>(&l);
+                } else {
+                    hi[e] = *reinterpret_cast<const uint16_t*>(&x);
+                }
+            }
+        }
+        uint16_t* dst = packed + ((((rb * kblocks + kb) * NPL) * 128u + r) * 32u + oct * 8u);
+        uint4 o;
+        o.x = hi[0] | ((uint32_t)hi[1] << 16);
+        o.y = hi[2] | ((uint32_t)hi[3] << 16);
+        o.z = hi[4] | ((uint32_t)hi[5] << 16);
+        o.w = hi[6] | ((uint32_t)hi[7] << 16);
+        *reinterpret_cast<uint4*>(dst) = o;
+        if (NPL == 2) {
+            o.x = lo[0] | ((uint32_t)lo[1] << 16);
+            o.y = lo[2] | ((uint32_t)lo[3] << 16);
+            o.z = lo[4] | ((uint32_t)lo[5] << 16);
+            o.w = lo[6] | ((uint32_t)lo[7] << 16);
+            *reinterpret_cast<uint4*>(dst + 128u * 32u) = o;
+        }
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+Packed packed_geometry(int dtype, int64_t rows, int64_t K) {
+    Packed g;
+    g.rowblocks = (uint32_t)((rows + 127) / 128);
+    g.kblocks = (uint32_t)((K + 31) / 32);
+    g.npl = dtype == TB_F32 ? 2u : 1u;
+    g.bytes = align_up((size_t)g.rowblocks * g.kblocks * g.npl * GTILE_BYTES, 1024);
+    return g;
+}
+
+int launch_pack(const void* src, int dtype, bool trans, uint64_t rows, uint64_t K, uint64_t ld,
+                       uint16_t* packed, const Packed& g, int sm_count, cudaStream_t stream) {
+    const uint64_t total = (uint64_t)g.rowblocks * g.kblocks * 512u;
+    uint64_t blocks = (total + 255) / 256;
+    const uint64_t cap = (uint64_t)sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    const uint32_t nb = (uint32_t)blocks;
+    if (dtype == TB_F32) {
+        const float* s = static_cast<const float*>(src);
+        if (trans)
+            pack_kernel<float, 2, true><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+        else
+            pack_kernel<float, 2, false><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+    } else {
+        const uint16_t* s = static_cast<const uint16_t*>(src);
+        if (trans)
+            pack_kernel<uint16_t, 1, true><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+        else
+            pack_kernel<uint16_t, 1, false><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+    }
+    TB_CUDA(cudaGetLastError());
+    return TB_OK;
+}
+
+static int packed_tmap(CUtensorMap* map, const uint16_t* packed, const Packed& g, int dtype) {
+    const uint64_t dims[2] = {GK, (uint64_t)g.rowblocks * g.kblocks * g.npl * 128u};
+    const uint64_t strides[1] = {GK * 2u};
+    const uint32_t box[2] = {GK, 128};
+    return encode_tmap(map, dtype == TB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                       2, packed, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+// C[M x N] (+)= alpha * row_scale[m] * Apacked . Bpacked^T
+int launch_gemm(int device, cudaStream_t stream, const uint16_t* pa, const Packed& ga,
+                       const uint16_t* pb, const Packed& gb, int dtype, int64_t M, int64_t N, float* C,
+                       int64_t ldc, const float* row_scale, float alpha, int accumulate, int symmetric) {
+    CUtensorMap map_a, map_b;
+    int rc = packed_tmap(&map_a, pa, ga, dtype);
+    if (rc != TB_OK) return rc;
+    rc = packed_tmap(&map_b, pb, gb, dtype);
+    if (rc != TB_OK) return rc;
+    GemmParams p;
+    p.C = C;
+    p.row_scale = row_scale;
+    p.status = status_ptr(device);
+    p.ldc = ldc;
+    p.M = (uint32_t)M;
+    p.N = (uint32_t)N;
+    p.kblocks = ga.kblocks;
+    p.idesc = idesc_f16(dtype == TB_F16 ? 0u : 1u, 256);
+    p.alpha = alpha;
+    p.accumulate = accumulate;
+    p.symmetric = symmetric;
+    const uint32_t stage_bytes = 4u * ga.npl * GTILE_BYTES;
+    p.stages = (200u * 1024u) / stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024u;
+    dim3 grid((uint32_t)((N + 255) / 256), (uint32_t)((M + 255) / 256), 1);
+    if (ga.npl == 2) {
+        auto kern = gemm_nt_kernel<2>;
+        TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, 384, smem, stream>>>(map_a, map_b, p);
+    } else {
+        auto kern = gemm_nt_kernel<1>;
+        TB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, 384, smem, stream>>>(map_a, map_b, p);
+    }
+    TB_CUDA(cudaGetLastError());
+    return TB_OK;
+}
+
+}  // namespace tb
+
+extern "C" {
+
+size_t tb_gemm_nt_workspace_bytes(int dtype, int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return tb::packed_geometry(dtype, M, K).bytes + tb::packed_geometry(dtype, N, K).bytes + 1024;
+}
+
+int tb_gemm_nt(int device, void* stream_, const void* A, int64_t lda, const void* B, int64_t ldb, int dtype,
+               int64_t M, int64_t N, int64_t K, float* C, int64_t ldc, const float* row_scale, float alpha,
+               int accumulate, void* ws, size_t ws_bytes) {
+    using namespace tb;
+    if (dtype != TB_F16 && dtype != TB_BF16 && dtype != TB_F32) return TB_ERR_BAD_DTYPE;
+    if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < K || ldc < N || M > 0x7fffffff || N > 0x7fffffff)
+        return TB_ERR_BAD_SHAPE;
+    if (!A || !B || !C) return TB_ERR_BAD_ARG;
+    if (!ws || ((uintptr_t)ws & 255u) != 0 || ws_bytes < tb_gemm_nt_workspace_bytes(dtype, M, N, K))
+        return TB_ERR_WORKSPACE;
+    int sm_count = 0;
+    int rc = select_device(device, &sm_count);
+    if (rc != TB_OK) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const Packed ga = packed_geometry(dtype, M, K), gb = packed_geometry(dtype, N, K);
+    if ((uint64_t)ga.rowblocks * ga.kblocks * ga.npl * 128u > 0x7fffffffull ||
+        (uint64_t)gb.rowblocks * gb.kblocks * gb.npl * 128u > 0x7fffffffull)
+        return TB_ERR_UNSUPPORTED;
+    uint16_t* pa = static_cast<uint16_t*>(ws);
+    uint16_t* pb = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(ws) + ga.bytes);
+    rc = launch_pack(A, dtype, false, M, K, lda, pa, ga, sm_count, stream);
+    if (rc != TB_OK) return rc;
+    rc = launch_pack(B, dtype, false, N, K, ldb, pb, gb, sm_count, stream);
+    if (rc != TB_OK) return rc;
+    return launch_gemm(device, stream, pa, ga, pb, gb, dtype, M, N, C, ldc, row_scale, alpha, accumulate, 0);
+}
+
+size_t tb_gram_workspace_bytes(int dtype, int64_t n, int64_t k) {
+    if (n <= 0 || k <= 0) return 0;
+    return tb::packed_geometry(dtype, k, n).bytes + 1024;
+}
+
+int tb_gram(int device, void* stream_, const void* X, int dtype, int64_t n, int64_t k, int64_t ld, float* G,
+            int64_t ldg, int accumulate, void* ws, size_t ws_bytes) {
+    using namespace tb;
+    if (dtype != TB_F16 && dtype != TB_BF16 && dtype != TB_F32) return TB_ERR_BAD_DTYPE;
+    if (n <= 0 || k <= 0 || ld < k || ldg < k || k > 0x7fffffff) return TB_ERR_BAD_SHAPE;
+    if (!X || !G) return TB_ERR_BAD_ARG;
+    if (!ws || ((uintptr_t)ws & 255u) != 0 || ws_bytes < tb_gram_workspace_bytes(dtype, n, k))
+        return TB_ERR_WORKSPACE;
+    int sm_count = 0;
+    int rc = select_device(device, &sm_count);
+    if (rc != TB_OK) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    // the operand is X^T: k operand rows, contraction over the n rows of X
+    const Packed g = packed_geometry(dtype, k, n);
+    if ((uint64_t)g.rowblocks * g.kblocks * g.npl * 128u > 0x7fffffffull) return TB_ERR_UNSUPPORTED;
+    uint16_t* px = static_cast<uint16_t*>(ws);
+    rc = launch_pack(X, dtype, true, k, n, ld, px, g, sm_count, stream);
+    if (rc != TB_OK) return rc;
+    return launch_gemm(device, stream, px, g, px, g, dtype, k, k, G, ldg, nullptr, 1.0f, accumulate, 1);
+}
+
+}  // extern "C"

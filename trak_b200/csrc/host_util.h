@@ -28,10 +28,12 @@ int select_device(int device, int* sm_count);
 // Device address of the status word of `device` (valid after select_device).
 uint32_t* status_ptr(int device);
 
-// Encodes a tiled tensor map (rank 2 or 3, 128-byte swizzle, zero fill).
+// Encodes a tiled tensor map (rank 2 or 3, zero fill; the box's inner extent must equal the
+// swizzle width).
 // dims / box are innermost first; strides_bytes has rank-1 entries.
 int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
-                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
+                const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 // Events armed by tb_profile_events for this thread (null when not armed); taking clears them.
 void take_profile_events(cudaEvent_t* before, cudaEvent_t* after);

@@ -17,6 +17,7 @@ enum : uint32_t {
     ST_TIMEOUT_FULL_B = 3,  // MMA issuer waited for a TMA tile
     ST_TIMEOUT_ACC = 4,     // epilogue waited for the accumulator
     ST_TIMEOUT_DRAIN = 5,   // teardown waited for copies in flight
+    ST_NOT_SPD = 6,         // Cholesky met a non-positive pivot (not a wait: the matrix is not SPD)
 };
 
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // 4 s per wait

@@ -1,0 +1,196 @@
+"""Score computer with the reference's interface, running on the sm_100a kernels.
+
+Mirrors ``BasicScoreComputer`` (trak/score_computers.py:114-189): same constructor
+arguments, same three methods, same shapes and dtypes of the results, so it can be
+passed to an unmodified ``TRAKer(score_computer=B200ScoreComputer)``
+(trak/traker.py:186-193).  Differences:
+
+* products run on the tensor cores (fp32 inputs as bf16 hi + lo planes, three passes);
+* the regularised inverse goes through Cholesky in fp32 instead of LU and raises
+  ``NotPositiveDefinite`` where the matrix is not positive definite;
+* Gram blocks are accumulated in fp32 whatever ``dtype`` is (the reference adds
+  them in ``dtype``) and cast once at the end;
+* with a ``process_group`` the Gram of this rank's rows is summed over the group
+  (one all-reduce of k x k fp32) -- rows sharded across GPUs, everything else
+  local: the inverse is replicated, features and scores stay row-sharded;
+* ``get_scores`` takes an optional ``row_scale`` (the out-to-loss weights) that is
+  applied inside the GEMM epilogue.
+
+There is no CPU path: tensors are moved to ``device`` and the CUDA library must load.
+"""
+import logging
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.TB_F16, torch.bfloat16: _lib.TB_BF16, torch.float32: _lib.TB_F32}
+_workspaces = {}
+
+
+def _workspace(device, stream, nbytes):
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        _workspaces.pop(key, None)
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def free_workspaces():
+    _workspaces.clear()
+
+
+def _as_device_matrix(t: torch.Tensor, device) -> torch.Tensor:
+    t = t.to(device, non_blocking=True)
+    if t.dtype not in _DTYPES:
+        t = t.float()
+    if t.dim() != 2:
+        raise RuntimeError("expected a 2-D tensor")
+    if t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        t = t.contiguous()
+    return t
+
+
+def gram(x: torch.Tensor, out: torch.Tensor = None, accumulate: bool = False) -> torch.Tensor:
+    """fp32 [k, k] = x^T x (+ out) for a CUDA matrix x [n, k] (fp16 / bf16 / fp32)."""
+    n, k = x.shape
+    dev = x.device
+    if out is None:
+        out = torch.empty((k, k), dtype=torch.float32, device=dev)
+        accumulate = False
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        dt = _DTYPES[x.dtype]
+        ws = _workspace(dev, stream, lib.tb_gram_workspace_bytes(dt, n, k))
+        _lib.check(lib.tb_gram(dev.index, stream, x.data_ptr(), dt, n, k, x.stride(0), out.data_ptr(),
+                               out.stride(0), int(accumulate), ws.data_ptr(), ws.numel()))
+    return out
+
+
+def spd_inverse_(a: torch.Tensor, lambda_reg: float = 0.0, rescale: bool = True) -> torch.Tensor:
+    """In place: a <- inv(a + lambda I) [/ mean |entry|] for a CUDA fp32 [k, k] matrix."""
+    if a.dtype != torch.float32 or a.dim() != 2 or a.shape[0] != a.shape[1] or a.stride(1) != 1:
+        raise RuntimeError("expected a square fp32 matrix with unit column stride")
+    dev = a.device
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ws = _workspace(dev, stream, lib.tb_spd_inverse_workspace_bytes(a.shape[0]))
+        _lib.check(lib.tb_spd_inverse(dev.index, stream, a.data_ptr(), a.shape[0], a.stride(0),
+                                      float(lambda_reg), int(rescale), None, ws.data_ptr(), ws.numel()))
+        _lib.device_status(dev.index)  # raises NotPositiveDefinite / DeviceTimeout
+    return a
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, row_scale: torch.Tensor = None,
+            alpha: float = 1.0, accumulate: bool = False) -> torch.Tensor:
+    """fp32 [M, N] = alpha * row_scale[:, None] * a @ b.T (+ out) for CUDA a [M, K], b [N, K]."""
+    if a.dtype != b.dtype:
+        a, b = a.float(), b.float()
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K:
+        raise RuntimeError("inner dimensions differ")
+    dev = a.device
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=dev)
+        accumulate = False
+    if row_scale is not None:
+        row_scale = row_scale.to(dev, torch.float32).reshape(-1).contiguous()
+        if row_scale.numel() != M:
+            raise RuntimeError("row_scale must have one entry per row of a")
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        dt = _DTYPES[a.dtype]
+        ws = _workspace(dev, stream, lib.tb_gemm_nt_workspace_bytes(dt, M, N, K))
+        _lib.check(lib.tb_gemm_nt(dev.index, stream, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), dt,
+                                  M, N, K, out.data_ptr(), out.stride(0),
+                                  row_scale.data_ptr() if row_scale is not None else None, float(alpha),
+                                  int(accumulate), ws.data_ptr(), ws.numel()))
+    return out
+
+
+class B200ScoreComputer:
+    """Drop-in for ``BasicScoreComputer`` on a B200."""
+
+    def __init__(self, dtype: torch.dtype, device, CUDA_MAX_DIM_SIZE: int = 65_536,
+                 logging_level=logging.INFO, lambda_reg: float = 0.0, process_group=None) -> None:
+        self.dtype = dtype
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError("B200ScoreComputer only works on a CUDA device")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        self.CUDA_MAX_DIM_SIZE = CUDA_MAX_DIM_SIZE  # rows moved to the GPU and multiplied at a time
+        self.logger = logging.getLogger("ScoreComputer")
+        self.logger.setLevel(logging_level)
+        self.lambda_reg = lambda_reg
+        self.process_group = process_group
+        _lib.lib()
+
+    # -- trak/score_computers.py:145-155
+    def get_xtx(self, grads: torch.Tensor) -> torch.Tensor:
+        self.proj_dim = grads.shape[1]
+        acc = None
+        for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
+            blk = _as_device_matrix(block, self.device)
+            acc = gram(blk, out=acc, accumulate=acc is not None)
+        acc = reduce_gram(acc, self.process_group)
+        _lib.device_status(self.device.index)
+        return acc.to(self.dtype)
+
+    # -- trak/score_computers.py:157-177
+    def get_x_xtx_inv(self, grads: torch.Tensor, xtx: torch.Tensor) -> torch.Tensor:
+        inv = xtx.to(self.device, torch.float32).clone()
+        spd_inverse_(inv, self.lambda_reg, rescale=True)
+        inv = inv.to(self.dtype)
+        result = torch.empty(grads.shape[0], inv.shape[1], dtype=self.dtype, device=self.device)
+        start = 0
+        for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
+            blk = _as_device_matrix(block, self.device)
+            # the inverse is symmetric, so block @ inv == block @ inv.T
+            result[start:start + blk.shape[0]] = gemm_nt(blk, inv.to(blk.dtype)).to(self.dtype)
+            start += blk.shape[0]
+        _lib.device_status(self.device.index)
+        return result
+
+    # -- trak/score_computers.py:179-189
+    def get_scores(self, features: torch.Tensor, target_grads: torch.Tensor, accumulator: torch.Tensor,
+                   row_scale: torch.Tensor = None) -> None:
+        targets = _as_device_matrix(target_grads, self.device)
+        start = 0
+        for block in torch.split(features, self.CUDA_MAX_DIM_SIZE, dim=0):
+            blk = _as_device_matrix(block, self.device)
+            rs = None if row_scale is None else row_scale.reshape(-1)[start:start + blk.shape[0]]
+            part = gemm_nt(blk, targets, row_scale=rs)
+            rows = slice(start, start + blk.shape[0])
+            if accumulator.device == part.device:
+                accumulator[rows] += part.to(accumulator.dtype)
+            else:
+                accumulator[rows] += part.to(accumulator.dtype).to(accumulator.device)
+            start += blk.shape[0]
+        _lib.device_status(self.device.index)
+
+
+def reduce_gram(local_gram: torch.Tensor, process_group=None) -> torch.Tensor:
+    """Sums the per-rank Gram matrices when the train rows are sharded over a process group
+    (the only exchange of the scoring path); a no-op for a single process."""
+    import torch.distributed as dist
+    if process_group is None:
+        return local_gram
+    if not (dist.is_available() and dist.is_initialized()):
+        raise RuntimeError("process_group given but torch.distributed is not initialised")
+    dist.all_reduce(local_gram, op=dist.ReduceOp.SUM, group=process_group)
+    return local_gram
+
+
+def shard_rows(n: int, rank: int, world: int):
+    """Contiguous row range [lo, hi) of rank `rank` when n rows are split over `world` ranks."""
+    base, rem = divmod(n, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
