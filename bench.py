@@ -9,6 +9,10 @@ Multi-GPU: one process per GPU (torchrun), every rank projects its own batch of
 128 examples with the same virtual matrix -- the path shards by example, there is
 no data-path collective (weak scaling).
 
+After the projection, the second hot path is measured too (key ``scoring`` of the same
+line): the whole C4 scoring job -- X fp32 [1,000,000 x 8192] sharded by rows over the GPUs,
+Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000 targets.
+
 Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
 HBM; ``e2e`` is the same through the public ``fast_jl.project_normal_32`` call with
 the batch in pinned host memory and the result read back; ``roofline`` rates the
@@ -154,6 +158,110 @@ def workload_config(D):
             "l2": "input batch (2.86 GB at full size) is larger than the 126 MB L2; no flush needed"}
 
 
+# ---- after-kernel scoring (second hot path) ---------------------------------------------------
+SC_N, SC_K, SC_M, SC_LAMBDA, SC_BLOCK = 1_000_000, 8192, 10_000, 1e-3, 65_536
+
+
+def scoring_flop(n, k, m):
+    """Algorithmic work of the whole job: symmetric Gram, inverse, features, scores."""
+    return n * k * (k + 1) + k ** 3 + 2.0 * n * k * k + 2.0 * n * m * k
+
+
+def run_scoring(args, dev, rank, world, scale):
+    """Train rows [n, k] fp32 sharded over the ranks: Gram per shard -> one all-reduce -> Cholesky
+    inverse with the mean-|.| rescale (replicated) -> features and out-to-loss-weighted scores for
+    m targets per shard.  Returns the timing of the whole job (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from trak_b200 import _lib, score_computers as sc
+
+    n_total = max(world * 1024, int(SC_N * scale))
+    lo, hi = sc.shard_rows(n_total, rank, world)
+    n = hi - lo
+    k, m = SC_K, max(256, int(SC_M * scale))
+    gen = torch.Generator(device=dev).manual_seed(2000 + rank)
+    X = torch.empty(n, k, device=dev)
+    for i in range(0, n, SC_BLOCK):  # generated block-wise to bound temporary memory
+        X[i:i + SC_BLOCK] = torch.randn(min(SC_BLOCK, n - i), k, device=dev, generator=gen) / k ** 0.5
+    T = torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(3000)) / k ** 0.5
+    w = torch.rand(n, device=dev, generator=torch.Generator(device=dev).manual_seed(4000 + rank))
+    scores = torch.empty(n, m, device=dev)
+    feats = torch.empty(min(SC_BLOCK, n), k, device=dev)
+    gram = torch.empty(k, k, device=dev)
+
+    def job():
+        for i in range(0, n, SC_BLOCK):
+            sc.gram(X[i:i + SC_BLOCK], out=gram, accumulate=i > 0)
+        if world > 1:
+            dist.all_reduce(gram)
+        sc.spd_inverse_(gram, SC_LAMBDA, rescale=True)  # gram now holds the rescaled inverse
+        for i in range(0, n, SC_BLOCK):
+            rows = min(SC_BLOCK, n - i)
+            sc.gemm_nt(X[i:i + rows], gram, out=feats[:rows])
+            sc.gemm_nt(feats[:rows], T, out=scores[i:i + rows], row_scale=w[i:i + rows])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    job()
+    barrier()
+    steps = 2
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        job()
+    ev1.record()
+    barrier()
+    _lib.device_status(dev.index)
+    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    sec = ms.item() * 1e-3
+    peak, _ = measured_peaks()
+    out = {"metric": "scoring_seconds", "value": sec, "unit": "s", "higher_is_better": False, "scaling": "strong",
+           "config": {"workload": f"C4 scoring: X fp32 [{n_total} x {k}] N(0,1/k) sharded by rows over {world} GPU(s), "
+                                  f"lambda {SC_LAMBDA}, {m} targets, out-to-loss weights fused",
+                      "row_block": SC_BLOCK},
+           "algorithmic_tflops": scoring_flop(n_total, k, m) / sec / 1e12,
+           "roofline": {"bound": "tensor", "achieved": scoring_flop(n_total, k, m) / sec / 1e12 / world, "peak": peak,
+                        "unit": "TFLOP/s", "frac": scoring_flop(n_total, k, m) / sec / 1e12 / world / peak,
+                        "note": "fp32 inputs run as bf16 hi/lo splits: three tensor-core passes per algorithmic flop, "
+                                "so 1/3 of the bf16 peak is the ceiling of this figure"}}
+    del X, scores, feats
+    torch.cuda.empty_cache()
+    return out
+
+
+def scoring_cpu_baseline(threads):
+    """CPU port of BasicScoreComputer on a bounded sample (k full, fewer rows and targets), scaled to C4."""
+    import torch
+    from oracle import basic_ref
+    torch.set_num_threads(threads)
+    n, k, m = 8192, SC_K, 512
+    X = torch.randn(n, k, generator=torch.Generator().manual_seed(1)) / k ** 0.5
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(2)) / k ** 0.5
+    t0 = time.perf_counter()
+    g = basic_ref.xtx(X)
+    t1 = time.perf_counter()
+    f = basic_ref.x_xtx_inv(X, g + (SC_N / n - 1) * torch.eye(k), SC_LAMBDA)  # keep the sample well conditioned
+    t2 = time.perf_counter()
+    acc = torch.zeros(n, m)
+    basic_ref.scores(f, T, acc)
+    t3 = time.perf_counter()
+    # Gram and features grow with n, scores with n*m; the inverse (part of t2 - t1) is size-independent:
+    # timed separately below
+    t4 = time.perf_counter()
+    basic_ref.xtx_inverse(g + (SC_N / n) * torch.eye(k), SC_LAMBDA)
+    t_inv = time.perf_counter() - t4
+    full = (t1 - t0) * SC_N / n + t_inv + max(0.0, (t2 - t1) - t_inv) * SC_N / n + (t3 - t2) * (SC_N / n) * (SC_M / m)
+    return {"value": full, "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"CPU port of BasicScoreComputer at k={k} on {n} rows x {m} targets "
+                      f"(gram {t1 - t0:.1f} s, inverse {t_inv:.1f} s, features {t2 - t1 - t_inv:.1f} s, scores {t3 - t2:.1f} s), "
+                      f"Gram/features scaled by n, scores by n*m, inverse counted once"}
+
+
 def run_ours(args, D):
     import torch
     import torch.distributed as dist
@@ -234,6 +342,10 @@ def run_ours(args, D):
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = world * ROWS / e2e_t.item()
     assert torch.equal(res_host, out.cpu()), "end-to-end result differs from the resident-input result"
+    del host_in, g_stage, g
+    fast_jl.free_workspaces()
+    torch.cuda.empty_cache()
+    scoring = None if args.no_scoring else run_scoring(args, dev, rank, world, args.scale)
 
     if rank == 0:
         peak, peak_note = measured_peaks()
@@ -255,6 +367,10 @@ def run_ours(args, D):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
         }
+        if scoring is not None:
+            line["scoring"] = scoring
+            if world == 1 and not args.no_cpu_baseline:
+                scoring["cpu_baseline"] = scoring_cpu_baseline(os.cpu_count() or 1)
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             sec, measured = cpu_port_sample(ROWS, D, threads, 2)
@@ -276,6 +392,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of D (profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-scoring", action="store_true", help="skip the after-kernel scoring measurement")
     args = ap.parse_args()
     D = max(1024, int(D_FULL * args.scale))
     if args.impl == "reference":
