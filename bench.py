@@ -151,10 +151,11 @@ def run_reference(args, D):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(D):
-    return {"workload": f"C2 gaussian JL projection: fp16 N(0,1e-2) grads [{ROWS} x {D}] per GPU -> k={K_DIM}, "
+def workload_config(D, proj_type="normal"):
+    name = "gaussian" if proj_type == "normal" else "rademacher"
+    return {"workload": f"C2 {name} JL projection: fp16 N(0,1e-2) grads [{ROWS} x {D}] per GPU -> k={K_DIM}, "
                         f"seed {SEED}, {TILES} feature tiles",
-            "rows_per_gpu": ROWS, "grad_dim": D, "proj_dim": K_DIM, "proj_type": "normal",
+            "rows_per_gpu": ROWS, "grad_dim": D, "proj_dim": K_DIM, "proj_type": proj_type,
             "l2": "input batch (2.86 GB at full size) is larger than the 126 MB L2; no flush needed"}
 
 
@@ -279,6 +280,7 @@ def run_ours(args, D):
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.lib()
 
+    ptype = _lib.TB_NORMAL if args.proj_type == "normal" else _lib.TB_RADEMACHER
     gen = torch.Generator(device=dev).manual_seed(1000 + rank)
     g = (torch.randn(ROWS, D, device=dev, generator=gen) * 1e-2).half()
     out = torch.empty(ROWS, K_DIM, device=dev, dtype=torch.float32)
@@ -286,7 +288,7 @@ def run_ours(args, D):
     def step(timed_events=None):
         if timed_events is not None:
             lib.tb_profile_events(timed_events[0].cuda_event, timed_events[1].cuda_event)
-        fast_jl.project(g, K_DIM, SEED, TILES, _lib.TB_NORMAL, out=out, strict=False)
+        fast_jl.project(g, K_DIM, SEED, TILES, ptype, out=out, strict=False)
 
     def barrier():
         if world > 1:
@@ -332,7 +334,7 @@ def run_ours(args, D):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         g_stage.copy_(host_in, non_blocking=True)
-        res = fast_jl.project_normal_32(g_stage, K_DIM, SEED, TILES)
+        res = getattr(fast_jl, f"project_{args.proj_type}_32")(g_stage, K_DIM, SEED, TILES)
         res_host = res.cpu()
         torch.cuda.synchronize()
         if i > 0:  # first iteration warms the pinned path
@@ -355,13 +357,14 @@ def run_ours(args, D):
             "metric": "jl_projected_examples_per_s", "value": value, "unit": "examples/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(D),
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(D, args.proj_type),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_FULL * D / D_FULL,
-                         "kernel": "project_kernel<normal>", "kernel_ms": kernel_ms,
+                         "kernel": f"project_kernel<{args.proj_type}>", "kernel_ms": kernel_ms,
                          "algorithmic_flop_per_launch": flop, "peak_source": peak_note,
-                         "note": "generator-issue-bound: the Gaussian matrix costs ~550 instructions per "
-                                 "16x32 tile, so the tensor pipe idles; see DESIGN.md"},
+                         "note": ("generator-issue-bound: the Gaussian matrix costs ~550 instructions per "
+                                  "16x32 tile, so the tensor pipe idles; see DESIGN.md") if ptype == _lib.TB_NORMAL
+                         else "MMA-bound under the power cap plus the restaging pass; see DESIGN.md"},
             "e2e": {"value": e2e_value, "unit": "examples/s", "h2d_bytes_per_step": ROWS * D * 2,
                     "d2h_bytes_per_step": ROWS * K_DIM * 4},
             "gpu_launches": 3 * args.steps,
@@ -391,6 +394,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of D (profiler captures)")
+    ap.add_argument("--proj-type", choices=["normal", "rademacher"], default="normal",
+                    help="normal = the benchmark workload; rademacher for profiling the other matrix type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scoring", action="store_true", help="skip the after-kernel scoring measurement")
     args = ap.parse_args()
