@@ -16,6 +16,7 @@
 namespace tb {
 
 constexpr int NB = 64;      // panel width
+constexpr int TRTRI_SPLIT = 16;  // most parts the triangular-inverse product is split into
 constexpr int TS = 68;      // padded row length of a shared-memory tile (floats)
 
 // acc[4][4] += sum_t At[t][ty*4 + i] * Bt[t][tx*4 + j]   (both tiles stored t-major)
@@ -85,14 +86,21 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, i
         }
         __syncthreads();
     }
-    // inverse of the lower-triangular block, one column per thread (forward substitution)
-    if (tid < jb) {
-        const int c = tid;
-        Winv[c][c] = 1.0f / S[c][c];
-        for (int i = c + 1; i < jb; ++i) {
+    // inverse of the lower-triangular block by forward substitution: column c is handled by the four
+    // lanes 4c..4c+3 of one warp, which split every dot product and combine with two shuffles
+    {
+        const int c = tid >> 2, part = tid & 3;
+        if (part == 0 && c < jb) Winv[c][c] = 1.0f / S[c][c];
+        __syncwarp();
+        for (int i = 1; i < jb; ++i) {
             float s = 0.0f;
-            for (int t = c; t < i; ++t) s = fmaf(S[i][t], Winv[t][c], s);
-            Winv[i][c] = -s / S[i][i];
+            if (c < i) {
+                for (int t = c + part; t < i; t += 4) s = fmaf(S[i][t], Winv[t][c], s);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (part == 0 && c < i) Winv[i][c] = -s / S[i][i];
+            __syncwarp();
         }
     }
     __syncthreads();
@@ -159,17 +167,18 @@ __global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float*
 }
 
 // Inverse, step 2:  W21[i, c] <- - sum_{t <= i} W22[i, t] * T[t, c]
-// W22 is the already inverted lower-triangular trailing block (r x r), T is r x jb; one CTA per
-// 64 rows, walking the tiles of its block row up to the diagonal.
-__global__ void __launch_bounds__(256) trtri_apply_kernel(const float* W22, float* W21, int64_t ld, const float* T,
-                                                          int64_t ldt, int r, int jb) {
+// W22 is the already inverted lower-triangular trailing block (r x r), T is r x jb.  The sum over
+// t is split: CTA (bi, sp) adds the tiles bt = sp, sp + nsplit, ... <= bi of block row bi into
+// part[sp][i][c]; trtri_reduce_kernel then adds the parts in a fixed order and negates.
+__global__ void __launch_bounds__(256) trtri_partial_kernel(const float* W22, int64_t ld, const float* T,
+                                                            int64_t ldt, int r, int jb, float* part) {
     __shared__ __align__(16) float At[NB][TS];
     __shared__ __align__(16) float Bt[NB][TS];
-    const int bi = blockIdx.x, i0 = bi * NB;
+    const int bi = blockIdx.x, i0 = bi * NB, sp = blockIdx.y, nsplit = gridDim.y;
     const int rows = min(NB, r - i0);
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     float acc[4][4] = {};
-    for (int bt = 0; bt <= bi; ++bt) {
+    for (int bt = sp; bt <= bi; bt += nsplit) {
         const int t0 = bt * NB, tcols = min(NB, r - t0);
         load_tile_T(At, W22 + (int64_t)i0 * ld + t0, ld, rows, tcols);
         if (bt == bi) {  // diagonal tile of a lower-triangular matrix: drop what lies above the diagonal
@@ -184,13 +193,24 @@ __global__ void __launch_bounds__(256) trtri_apply_kernel(const float* W22, floa
         tile_mma(At, Bt, ty, tx, acc);
         __syncthreads();
     }
+    float* dst = part + ((size_t)sp * r + i0) * NB;
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int ii = ty * 4 + i, c = tx * 4 + j;
-            if (ii < rows && c < jb) W21[(int64_t)(i0 + ii) * ld + c] = -acc[i][j];
+            if (ii < rows) dst[(size_t)ii * NB + c] = acc[i][j];
         }
+}
+__global__ void trtri_reduce_kernel(const float* part, int nsplit, int r, int jb, float* W21, int64_t ld) {
+    const int total = r * NB;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int i = e >> 6, c = e & 63;
+        if (c >= jb) continue;
+        float s = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) s += part[((size_t)sp * r + i) * NB + c];
+        W21[(int64_t)i * ld + c] = -s;
+    }
 }
 
 // A[j0.., j0..] diagonal block <- dinv block (lower), and zero the strict upper triangle of the
@@ -246,7 +266,7 @@ __global__ void scale_by_inverse_kernel(float* A, int64_t lda, int k, const floa
 }
 
 struct InvLayout {
-    size_t dinv, tbuf, partial, mean, packed, total;
+    size_t dinv, tbuf, tpart, partial, mean, packed, total;
 };
 static InvLayout inv_layout(int64_t k) {
     InvLayout l;
@@ -256,6 +276,8 @@ static InvLayout inv_layout(int64_t k) {
     off += align_up(nblk * NB * NB * sizeof(float), 256);
     l.tbuf = off;
     off += align_up((size_t)k * NB * sizeof(float), 256);
+    l.tpart = off;
+    off += align_up((size_t)TRTRI_SPLIT * k * NB * sizeof(float), 256);
     l.partial = off;
     off += align_up(RED_BLOCKS * sizeof(double), 256);
     l.mean = off;
@@ -289,6 +311,7 @@ int tb_spd_inverse(int device, void* stream_, float* A, int64_t k, int64_t lda, 
     uint8_t* base = static_cast<uint8_t*>(ws);
     float* dinv = reinterpret_cast<float*>(base + l.dinv);
     float* tbuf = reinterpret_cast<float*>(base + l.tbuf);
+    float* tpart = reinterpret_cast<float*>(base + l.tpart);
     double* partial = reinterpret_cast<double*>(base + l.partial);
     float* mean = reinterpret_cast<float*>(base + l.mean);
     uint16_t* packed = reinterpret_cast<uint16_t*>(base + l.packed);
@@ -319,7 +342,12 @@ int tb_spd_inverse(int device, void* stream_, float* A, int64_t k, int64_t lda, 
             float* L21 = A + (int64_t)(j0 + jb) * lda + j0;
             const int rt = (r + NB - 1) / NB;
             panel_kernel<1><<<rt, 256, 0, stream>>>(L21, lda, r, jb, D, tbuf, NB);
-            trtri_apply_kernel<<<rt, 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, L21, lda, tbuf, NB, r, jb);
+            int nsplit = (2 * sm_count + rt - 1) / rt;  // about two CTAs per SM
+            if (nsplit > TRTRI_SPLIT) nsplit = TRTRI_SPLIT;
+            if (nsplit > rt) nsplit = rt;
+            trtri_partial_kernel<<<dim3(rt, nsplit), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, lda, tbuf,
+                                                                         NB, r, jb, tpart);
+            trtri_reduce_kernel<<<(r * NB + 255) / 256, 256, 0, stream>>>(tpart, nsplit, r, jb, L21, lda);
         }
         write_diag_inverse_kernel<<<1, 256, 0, stream>>>(A, lda, K, j0, jb, D);
     }
