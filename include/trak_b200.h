@@ -89,6 +89,28 @@ int tb_project(int device, void *stream, const void *grads, int dtype, int64_t B
                uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate, void *ws,
                size_t ws_bytes);
 
+/* The same projection fed straight from the per-parameter gradient tensors, so that no
+ * [B, D] copy has to be assembled first (the reference concatenates them with
+ * vectorize(), trak/utils.py:80-110, and ChunkedCudaProjector copies them into a staging
+ * buffer, trak/projectors.py:501-502).  The gradient vector of sample b is the
+ * concatenation, in table order, of segs[i].numel elements starting at
+ * segs[i].ptr + b * segs[i].row_stride (elements of `dtype`, device memory, any alignment);
+ * F is the sum of the numel.  The table itself is host memory and may be released when the
+ * call returns.  Everything else as in tb_project. */
+typedef struct tb_segment {
+    const void *ptr;
+    int64_t numel;
+    int64_t row_stride;
+} tb_segment;
+
+size_t tb_project_segments_workspace_bytes(int dtype, int64_t B, int64_t F, uint32_t N,
+                                           uint32_t num_feature_tiles, int32_t nsegs);
+
+int tb_project_segments(int device, void *stream, const tb_segment *segs, int32_t nsegs, int dtype,
+                        int64_t B, float *out, int64_t ld_out, uint32_t N, uint32_t seed,
+                        uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate,
+                        void *ws, size_t ws_bytes);
+
 /* ---- after-kernel scoring -------------------------------------------------------
  * The three products and the inverse of the reference's BasicScoreComputer
  * (trak/score_computers.py:114-189).  Matrices are row-major; `dtype` is the type of

@@ -207,6 +207,25 @@ def test_projector_classes(cuda):
     assert got.shape == (6, 1024)
 
 
+@pytest.mark.parametrize("dt", ["f16", "f32", "bf16"])
+@pytest.mark.parametrize("B", [5, 140])
+def test_segments_equal_concatenation(cuda, dt, B):
+    """Projecting straight from per-parameter tensors gives the bits of projecting their concatenation."""
+    from trak_b200 import fast_jl
+    torch.manual_seed(B)
+    shapes = [(64, 3, 3, 3), (), (17,), (129, 31), (1,), (300, 7, 2), (5,)]   # () and (n,) as vectorize sees them
+    tensors = [torch.randn((B,) + sh, device=cuda).to(DT[dt]) for sh in shapes]
+    flat = torch.cat([t.reshape(B, 1) if t.dim() < 2 else t.flatten(start_dim=1) for t in tensors], dim=1)
+    for p in (RAD, NOR):
+        a = fast_jl.project_segments(tensors, 1024, 21, 148, p)
+        b = fast_jl.project(flat.contiguous(), 1024, 21, 148, p)
+        assert torch.equal(a, b)
+    out = torch.ones(B, 512, device=cuda)
+    fast_jl.project_segments(tensors, 512, 3, 148, RAD, alpha=2.0, out=out, accumulate=True)
+    torch.testing.assert_close(out, 1.0 + 2.0 * fast_jl.project(flat.contiguous(), 512, 3, 148, RAD),
+                               rtol=1e-6, atol=1e-4)
+
+
 def test_full_size_properties(cuda):
     """The benchmark's shape (128 x 11,173,962 fp16 -> 4096, 148 tiles): matrix rows at the far end
     of the feature range against the oracle, linearity and run-to-run identity."""

@@ -22,6 +22,13 @@ _lock = threading.Lock()
 
 _i, _i64, _u32 = ctypes.c_int, ctypes.c_int64, ctypes.c_uint32
 _vp, _sz, _f = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
+_i32 = ctypes.c_int32
+
+
+class Segment(ctypes.Structure):
+    """tb_segment: one parameter's per-sample gradients ([B, numel], rows row_stride apart)."""
+    _fields_ = [("ptr", ctypes.c_void_p), ("numel", ctypes.c_int64), ("row_stride", ctypes.c_int64)]
+
 
 # name -> (restype, argtypes); one entry per function include/trak_b200.h declares
 SIGNATURES = {
@@ -31,6 +38,9 @@ SIGNATURES = {
     "tb_device_status": (_i, [_i, ctypes.POINTER(_u32)]),
     "tb_project_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32]),
     "tb_profile_events": (_i, [_vp, _vp]),
+    "tb_project_segments_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32, _i32]),
+    "tb_project_segments": (_i, [_i, _vp, ctypes.POINTER(Segment), _i32, _i, _i64, _vp, _i64, _u32, _u32, _u32,
+                                 _i, _f, _i, _vp, _sz]),
     "tb_gram_workspace_bytes": (_sz, [_i, _i64, _i64]),
     "tb_gram": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _i, _vp, _sz]),
     "tb_spd_inverse_workspace_bytes": (_sz, [_i64]),

@@ -99,6 +99,58 @@ def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None
     return out
 
 
+def project_segments(tensors, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None, accumulate=False,
+                     strict=None):
+    """Projects the per-sample gradient whose sample b is the concatenation of ``t[b].reshape(-1)`` over
+    ``tensors`` (a list of CUDA tensors ``[B, *shape]``, one dtype, each with contiguous samples) without
+    first copying them into one ``[B, D]`` matrix.  A tensor with fewer than two dimensions contributes one
+    feature per sample, as in the reference's ``vectorize`` (trak/utils.py:100-102).  Same result as
+    ``project(torch.cat([t.reshape(B, -1) for t in tensors], 1), ...)``."""
+    if not tensors:
+        raise RuntimeError("no gradient tensors")
+    first = tensors[0]
+    B, dev, dtype = first.shape[0], first.device, first.dtype
+    if dtype not in _DTYPES or not first.is_cuda:
+        raise RuntimeError("gradients must be CUDA tensors of dtype fp16, bf16 or fp32")
+    N = _u32("N", N)
+    seed = _u32("seed", seed)
+    num_feature_tiles = _u32("num_feature_tiles", num_feature_tiles)
+    segs = (_lib.Segment * len(tensors))()
+    keep = []
+    F = 0
+    for i, t in enumerate(tensors):
+        if t.device != dev or t.dtype != dtype or t.shape[0] != B:
+            raise RuntimeError("all gradient tensors must share device, dtype and batch size")
+        flat = t.reshape(B, 1) if t.dim() < 2 else t.flatten(start_dim=1)
+        if flat.shape[1] == 0:
+            raise RuntimeError("empty parameter")
+        if flat.stride(1) != 1 or (B > 1 and flat.stride(0) < flat.shape[1]):
+            flat = flat.contiguous()
+        keep.append(flat)
+        segs[i].ptr = flat.data_ptr()
+        segs[i].numel = flat.shape[1]
+        segs[i].row_stride = flat.stride(0) if B > 1 else flat.shape[1]
+        F += flat.shape[1]
+    l = _lib.lib()
+    if out is None:
+        out = torch.empty((B, N), dtype=torch.float32, device=dev)
+        accumulate = False
+    elif out.device != dev or out.dtype != torch.float32 or tuple(out.shape) != (B, N) or out.stride(1) != 1:
+        raise RuntimeError("out must be a float32 [B, N] tensor on the gradients' device")
+    dt = _DTYPES[dtype]
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        nbytes = l.tb_project_segments_workspace_bytes(dt, B, F, N, max(num_feature_tiles, 1), len(tensors))
+        ws = _workspace(dev, stream, max(nbytes, 256))
+        rc = l.tb_project_segments(dev.index, stream, segs, len(tensors), dt, B, out.data_ptr(), out.stride(0), N,
+                                   seed, num_feature_tiles, int(proj_type), float(alpha), int(bool(accumulate)),
+                                   ws.data_ptr(), ws.numel())
+        _lib.check(rc)
+        if _STRICT if strict is None else strict:
+            _lib.device_status(dev.index)
+    return out
+
+
 def project_rademacher_8(input, N, seed, num_feature_tiles):
     return project(input, N, seed, num_feature_tiles, _lib.TB_RADEMACHER)
 

@@ -49,6 +49,12 @@ def vectorize(g: dict, device="cuda") -> torch.Tensor:
     return out
 
 
+def _segmentable(vals, device) -> bool:
+    d = torch.device(device)
+    return all(v.is_cuda and v.device == d and v.dtype == vals[0].dtype for v in vals) and \
+        vals[0].dtype in (torch.float16, torch.bfloat16, torch.float32)
+
+
 class CudaProjector:
     """JL projection on a B200.  ``max_batch_size`` is accepted for signature
     compatibility; the kernels take any batch and ignore it."""
@@ -80,9 +86,15 @@ class CudaProjector:
 
     def project(self, grads: Union[dict, torch.Tensor], model_id: int, *, alpha: float = 1.0,
                 out: torch.Tensor = None, accumulate: bool = False) -> torch.Tensor:
+        seed = (self.seed + int(1e4) * model_id) & 0xFFFFFFFF
         if isinstance(grads, dict):
+            vals = list(grads.values())
+            if _segmentable(vals, self.device):
+                # straight from the per-parameter tensors: no [B, D] copy (trak/utils.py:80-110)
+                return _fast_jl.project_segments(vals, self.proj_dim, seed, self.num_sms, self._ptype,
+                                                 alpha=alpha, out=out, accumulate=accumulate)
             grads = vectorize(grads, device=self.device)
-        return _fast_jl.project(grads, self.proj_dim, (self.seed + int(1e4) * model_id) & 0xFFFFFFFF,
+        return _fast_jl.project(grads, self.proj_dim, seed,
                                 self.num_sms, self._ptype, alpha=alpha, out=out,
                                 accumulate=accumulate, allow_strided=True)
 
@@ -126,6 +138,23 @@ class ChunkedCudaProjector:
         del self.ch_input
         self.input_allocated = False
 
+    def _project_direct(self, vals, rows, model_id, out):
+        """Same chunking rule, but every chunk is projected straight from its parameters' tensors
+        (no packing into ch_input) and accumulated into `out` by the kernel."""
+        chunk, width, index = [], 0, 0
+        for p in vals:
+            w = 1 if p.dim() < 2 else p[0].numel()
+            if width + w > self.max_chunk_size:
+                assert width == self.params_per_chunk[index]
+                self.projector_per_chunk[index].project(dict(enumerate(chunk)), model_id, out=out,
+                                                        accumulate=index > 0)
+                chunk, width, index = [], 0, index + 1
+            chunk.append(p[:rows])
+            width += w
+        assert width == self.params_per_chunk[index]
+        self.projector_per_chunk[index].project(dict(enumerate(chunk)), model_id, out=out, accumulate=index > 0)
+        return out.to(self.dtype)
+
     def _flush(self, index, rows, pointer, model_id, out, first):
         assert pointer == self.params_per_chunk[index]
         proj = self.projector_per_chunk[index]
@@ -138,10 +167,13 @@ class ChunkedCudaProjector:
             out.copy_(res) if first else out.add_(res)
 
     def project(self, grads, model_id):
-        self.allocate_input()
         vals = list(grads.values())
         rows = min(self.feat_bs, vals[0].shape[0])
         out = torch.empty((rows, self.proj_dim), device=self.device, dtype=torch.float32)
+        if all(isinstance(p, CudaProjector) for p in self.projector_per_chunk) and \
+                _segmentable(vals, self.device):
+            return self._project_direct(vals, rows, model_id, out)
+        self.allocate_input()
         pointer, index, first = 0, 0, True
         for p in vals:
             flat = p.data.unsqueeze(-1) if p.dim() < 2 else p.data.flatten(start_dim=1)
