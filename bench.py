@@ -14,8 +14,9 @@ line): the whole C4 scoring job -- X fp32 [1,000,000 x 8192] sharded by rows ove
 Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000 targets.
 
 Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
-HBM; ``e2e`` is the same through the public ``fast_jl.project_normal_32`` call with
-the batch in pinned host memory and the result read back; ``roofline`` rates the
+HBM; ``e2e`` is the same through the public ``trak_b200.fast_jl.project`` call with every
+step's batch copied from pinned host memory and its result read back (the copy of the next
+batch overlaps the current projection); ``roofline`` rates the
 projection kernel against the tensor-core peak; ``cpu_baseline`` is the CPU port of
 the reference's BasicProjector timed on a bounded sample on this box.
 
@@ -71,7 +72,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -324,26 +325,52 @@ def run_ours(args, D):
     value = world * ROWS * args.steps / (ms_total * 1e-3)
 
     # ---- end to end through the public entry point, host buffers -------------------------
-    e2e_steps = max(1, min(args.steps, 3))
+    # Every step copies its own batch from pinned host memory and reads its own result back.
+    # Two device buffers: the copy of step i+1 runs on a side stream while step i projects
+    # (what a featurize loop over a data loader does); all of it is inside the timed region.
+    e2e_steps = max(2, min(args.steps, 6))
     host_in = torch.empty(ROWS, D, dtype=torch.float16).pin_memory()
     host_in.copy_(g)
-    g_stage = torch.empty_like(g)
+    host_out = torch.empty(ROWS, K_DIM, dtype=torch.float32).pin_memory()
+    bufs = [g, torch.empty_like(g)]
+    copy_stream = torch.cuda.Stream(device=dev)
+
+    def e2e_run(n_steps):
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        free = [torch.cuda.Event(), torch.cuda.Event()]
+        main = torch.cuda.current_stream(dev)
+        with torch.cuda.stream(copy_stream):
+            bufs[0].copy_(host_in, non_blocking=True)
+            ready[0].record(copy_stream)
+        res = None
+        for i in range(n_steps):
+            cur, nxt = i % 2, (i + 1) % 2
+            if i + 1 < n_steps:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(free[nxt])  # step i-1 has finished reading that buffer
+                    bufs[nxt].copy_(host_in, non_blocking=True)
+                    ready[nxt].record(copy_stream)
+            main.wait_event(ready[cur])
+            res = fast_jl.project(bufs[cur], K_DIM, SEED, TILES, ptype, strict=False)
+            free[cur].record(main)
+            host_out.copy_(res, non_blocking=True)       # the step's result goes back to the host
+        torch.cuda.synchronize()
+        return res
+
+    e2e_run(2)  # warms the pinned path
+    _lib.device_status(local)
     barrier()
-    t_e2e = []
-    for i in range(e2e_steps + 1):
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        g_stage.copy_(host_in, non_blocking=True)
-        res = getattr(fast_jl, f"project_{args.proj_type}_32")(g_stage, K_DIM, SEED, TILES)
-        res_host = res.cpu()
-        torch.cuda.synchronize()
-        if i > 0:  # first iteration warms the pinned path
-            t_e2e.append(time.perf_counter() - t0)
-    e2e_t = torch.tensor([sum(t_e2e) / len(t_e2e)], device=dev)
+    t0 = time.perf_counter()
+    e2e_run(e2e_steps)
+    e2e_sec = (time.perf_counter() - t0) / e2e_steps
+    _lib.device_status(local)
+    e2e_t = torch.tensor([e2e_sec], device=dev)
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = world * ROWS / e2e_t.item()
-    assert torch.equal(res_host, out.cpu()), "end-to-end result differs from the resident-input result"
+    assert torch.equal(host_out, out.cpu()), "end-to-end result differs from the resident-input result"
+    g_stage = bufs[1]
     del host_in, g_stage, g
     fast_jl.free_workspaces()
     torch.cuda.empty_cache()

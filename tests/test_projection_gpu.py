@@ -258,6 +258,18 @@ def test_full_size_properties(cuda):
     assert np.all(np.abs(ratio - 1) < 0.05)
 
 
+def test_large_feature_count_and_projection_dim(cuda):
+    """A shape from the reference's overflow tests (tests/test_jl.py:59-73: F = 180,645,096, k = 15,360):
+    64-bit addressing in the restaging pass and matrix rows deep inside long feature tiles."""
+    F, N, seed, T = 180_645_096, 15_360, 123, 148
+    fts = o.feature_tile_size(F, T)
+    feats = [0, fts - 1, 5 * fts + 12_345, F - 1]
+    g = one_hot(8, F, feats, torch.float32, cuda)
+    out = ours(g, N, seed, T, RAD)
+    assert np.array_equal(out[:4].cpu().numpy(), o.matrix_rows(RAD, F, N, seed, T, feats))
+    assert float(out[4:].abs().max()) == 0.0
+
+
 # ---- against the compiled reference kernel itself, when it travelled with the repo ----
 
 def _witness():
