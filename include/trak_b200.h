@@ -58,6 +58,12 @@ const char *tb_last_cuda_error(void);
  * *detail, if not null, receives the raw status word. */
 int tb_device_status(int device, uint32_t *detail);
 
+/* Failure-path self-test (no counterpart in the reference): launches one CTA that waits, with the
+ * same bounded wait the pipelines use, on a barrier nothing arrives at.  After `limit_ms`
+ * (1..2000) the wait gives up and records the time-out; the next tb_device_status returns
+ * TB_ERR_DEVICE_TIMEOUT and the device stays usable.  Nothing faults, traps or hangs. */
+int tb_selftest_wait_timeout(int device, void *stream, uint32_t limit_ms);
+
 /* ---- JL projection ---------------------------------------------------------
  * out[b, n] = alpha * sum_f grads[b, f] * P[f, n]   (+ out[b, n] if accumulate)
  *

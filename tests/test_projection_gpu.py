@@ -294,6 +294,23 @@ def test_bit_exact_matrix_and_parity_vs_reference_kernel(cuda, B, F, N, seed, T)
             assert rel_rows(ours(g, N, seed, T, p).cpu().numpy(), ref_fn(g, N, seed, T).cpu().numpy()) <= TOL
 
 
+def test_bounded_wait_times_out_and_device_stays_usable(cuda):
+    """Failure detection without a fault: a wait that nothing satisfies gives up after its limit, the
+    status word reports it, and the next call works."""
+    import time
+    from trak_b200 import _lib, fast_jl
+    lib = _lib.lib()
+    _lib.device_status(cuda.index)
+    t0 = time.time()
+    assert lib.tb_selftest_wait_timeout(cuda.index, None, 100) == 0
+    with pytest.raises(_lib.DeviceTimeout):
+        _lib.device_status(cuda.index)
+    assert 0.09 < time.time() - t0 < 5.0
+    _lib.device_status(cuda.index)                      # the word was cleared
+    g = torch.ones(8, 1024, dtype=torch.float16, device=cuda)
+    assert np.all(np.mod(fast_jl.project_rademacher_8(g, 512, 0, 148).cpu().numpy(), 2) == 0)
+
+
 def test_device_status_clean(cuda):
     from trak_b200 import _lib
     _lib.device_status(cuda.index)

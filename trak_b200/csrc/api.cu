@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "host_util.h"
+#include "ptx.cuh"
 
 namespace tb {
 
@@ -54,6 +55,29 @@ int select_device(int device, int* sm_count) {
 }
 
 uint32_t* status_ptr(int device) { return g_dev_status_ptr[device]; }
+
+// One CTA waits, with the kernels' own bounded wait, on an mbarrier that nothing will ever arrive
+// at; when the limit runs out it records the failure exactly as the pipelines do and returns.
+__global__ void selftest_wait_kernel(uint32_t* status, uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_word = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        volatile uint32_t* abort_flag = &abort_word;
+        if (!mbar_wait(smem_u32(&bar), 0u, abort_flag, limit_ns)) {
+            if (atomicCAS(status, 0u, (uint32_t)ST_TIMEOUT_EMPTY) == 0u) {
+                status[1] = 0xFFFFFFFFu;  // marks the self-test
+                status[2] = 0;
+            }
+        }
+    }
+    __syncthreads();
+}
 
 typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -127,6 +151,16 @@ const char* tb_last_cuda_error(void) { return tb::t_cuda_error; }
 int tb_profile_events(void* before, void* after) {
     tb::t_ev_before = static_cast<cudaEvent_t>(before);
     tb::t_ev_after = static_cast<cudaEvent_t>(after);
+    return TB_OK;
+}
+
+int tb_selftest_wait_timeout(int device, void* stream, uint32_t limit_ms) {
+    if (limit_ms == 0 || limit_ms > 2000) return TB_ERR_BAD_ARG;
+    int rc = tb::select_device(device, nullptr);
+    if (rc != TB_OK) return rc;
+    tb::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(tb::status_ptr(device),
+                                                                              (uint64_t)limit_ms * 1000000ull);
+    TB_CUDA(cudaGetLastError());
     return TB_OK;
 }
 

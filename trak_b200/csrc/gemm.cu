@@ -76,7 +76,15 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ uint32_t abort_word;
     volatile uint32_t* abort_flag = &abort_word;
 
-    const uint32_t tile_m = blockIdx.y, tile_n = blockIdx.x;
+    // Tile order: CTAs are numbered so that the ~148 that run together cover a block of about
+    // 12 x 12 tiles (12 row panels of A and 12 of B share L2) instead of a few rows of all columns.
+    constexpr uint32_t GROUP_M = 12;
+    const uint32_t tiles_n = gridDim.x, tiles_m = gridDim.y;
+    const uint32_t id = blockIdx.y * tiles_n + blockIdx.x;
+    const uint32_t width = GROUP_M * tiles_n;
+    const uint32_t first_m = (id / width) * GROUP_M;
+    const uint32_t gsize = min(tiles_m - first_m, GROUP_M);
+    const uint32_t tile_m = first_m + (id % width) % gsize, tile_n = (id % width) / gsize;
     if (p.symmetric && tile_n < tile_m) return;  // whole CTA leaves before any barrier or TMEM use
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -74,14 +74,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out or another role of the
 // CTA has already given up (abort_flag, in shared memory, non-zero).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+                                          volatile uint32_t* abort_flag,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) return false;
+            if (globaltimer_ns() - t0 > limit_ns) return false;
         }
     }
 }
