@@ -44,8 +44,10 @@ def test_project_workspace_query():
     assert 0 < small < big
     # staged copy (128 rows x 148 tiles x 75520 padded features x 2 B) + partials
     assert big >= 128 * 148 * 75520 * 2
-    # more than 128 rows are walked 128 at a time: the workspace does not grow
-    assert lib.tb_project_workspace_bytes(0, 1024, 11173962, 4096, 148) == big
+    # batches are walked at most 256 rows at a time: the workspace stops growing there
+    big256 = lib.tb_project_workspace_bytes(0, 256, 11173962, 4096, 148)
+    assert big < big256 <= 2 * big
+    assert lib.tb_project_workspace_bytes(0, 1024, 11173962, 4096, 148) == big256
 
 
 def _call(**kw):
