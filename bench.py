@@ -46,7 +46,7 @@ BLOCK = 100  # BasicProjector's column block (trak/projectors.py:229)
 # DRAM traffic of one projection-kernel launch on the full workload, from the ncu
 # capture summarised in profiles/project_kernel_normal_small.md (dram__bytes_read.sum +
 # dram__bytes_write.sum at D/10, which grows in proportion to D, times 10)
-NCU_TRAFFIC_BYTES_FULL = 3.66e9
+NCU_TRAFFIC_BYTES_FULL = 3.53e9
 
 
 def measured_peaks():
