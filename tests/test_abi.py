@@ -80,3 +80,37 @@ def test_check_maps_codes_to_reference_exception_types():
     with pytest.raises(_lib.DeviceTimeout):
         _lib.check(7)
     _lib.check(0)
+
+
+def test_scoring_workspace_queries_and_validation():
+    lib = _lib.lib()
+    assert lib.tb_gram_workspace_bytes(2, 0, 10) == 0
+    # packed X^T: k rows x n, bf16 hi + lo planes = 4 bytes per element (rounded up to 128 x 32 tiles)
+    assert lib.tb_gram_workspace_bytes(2, 65536, 8192) >= 65536 * 8192 * 4
+    assert lib.tb_gram_workspace_bytes(0, 65536, 8192) >= 65536 * 8192 * 2
+    assert lib.tb_gemm_nt_workspace_bytes(2, 1000, 500, 64) >= (1024 + 512) * 64 * 4
+    assert lib.tb_spd_inverse_workspace_bytes(8192) >= 8192 * 8192 * 4
+    big = 1 << 40
+    # rejected on the host, before any CUDA call
+    assert lib.tb_gram(0, None, 0x1000, 9, 10, 10, 10, 0x2000, 10, 0, 0x10000, big) == 1     # dtype
+    assert lib.tb_gram(0, None, 0x1000, 2, 10, 10, 5, 0x2000, 10, 0, 0x10000, big) == 2      # ld < k
+    assert lib.tb_gram(0, None, None, 2, 10, 10, 10, 0x2000, 10, 0, 0x10000, big) == 4       # null input
+    assert lib.tb_gram(0, None, 0x1000, 2, 10, 10, 10, 0x2000, 10, 0, None, big) == 5        # no workspace
+    assert lib.tb_spd_inverse(0, None, 0x1000, 0, 10, 0.0, 1, None, 0x10000, big) == 2
+    assert lib.tb_spd_inverse(0, None, None, 10, 10, 0.0, 1, None, 0x10000, big) == 4
+    assert lib.tb_spd_inverse(0, None, 0x1000, 10, 10, 0.0, 1, None, 0x10000, 16) == 5
+    assert lib.tb_gemm_nt(0, None, 0x1000, 8, 0x2000, 8, 2, 4, 4, 8, 0x3000, 2, None, 1.0, 0, 0x10000, big) == 2  # ldc < N
+    assert lib.tb_gemm_nt(0, None, 0x1000, 8, None, 8, 2, 4, 4, 8, 0x3000, 4, None, 1.0, 0, 0x10000, big) == 4
+
+
+def test_segment_table_validation():
+    lib = _lib.lib()
+    segs = (_lib.Segment * 2)()
+    segs[0].ptr, segs[0].numel, segs[0].row_stride = 0x1000, 10, 10
+    segs[1].ptr, segs[1].numel, segs[1].row_stride = 0x2000, 5, 4          # stride < numel
+    big = 1 << 40
+    assert lib.tb_project_segments(0, None, segs, 2, 0, 4, 0x3000, 512, 512, 0, 148, 0, 1.0, 0, 0x10000, big) == 2
+    segs[1].row_stride = 5
+    assert lib.tb_project_segments(0, None, segs, 0, 0, 4, 0x3000, 512, 512, 0, 148, 0, 1.0, 0, 0x10000, big) == 4
+    assert lib.tb_project_segments(0, None, segs, 2, 0, 4, 0x3000, 512, 500, 0, 148, 0, 1.0, 0, 0x10000, big) == 3
+    assert lib.tb_project_segments_workspace_bytes(0, 4, 15, 512, 148, 2) > lib.tb_project_workspace_bytes(0, 4, 15, 512, 148)
