@@ -372,7 +372,7 @@ def run_ours(args, D):
     # Every step copies its own batch from pinned host memory and reads its own result back.
     # Two device buffers: the copy of step i+1 runs on a side stream while step i projects
     # (what a featurize loop over a data loader does); all of it is inside the timed region.
-    e2e_steps = max(2, min(args.steps, 6))
+    e2e_steps = max(2, min(args.steps, 20))
     host_in = torch.empty(ROWS, D, dtype=torch.float16).pin_memory()
     host_in.copy_(g)
     host_out = torch.empty(ROWS, K_DIM, dtype=torch.float32).pin_memory()
