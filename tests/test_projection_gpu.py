@@ -258,6 +258,39 @@ def test_full_size_properties(cuda):
     assert np.all(np.abs(ratio - 1) < 0.05)
 
 
+def test_randomised_shapes_against_oracle_rows_and_projection(cuda):
+    """Forty seeded random shapes (feature counts around tile and stage boundaries, tile counts that leave the
+    generator groups uneven work, batches on both sides of the 64 / 128 / 256-row shape switches): matrix rows
+    bit-exact (Rademacher), projections within tolerance (both types)."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        T = int(rng.choice([1, 2, 3, 5, 7, 37, 108, 148, 149, 1000]))
+        F = int(rng.choice([1, 15, 16, 17, 63, 64, 65, 1000, 4097, 9472, 9473, 75_531, 200_003]))
+        N = int(rng.choice([512, 1024, 2560]))
+        B = int(rng.choice([1, 7, 16, 17, 64, 65, 128, 129, 200, 257, 300]))
+        if B * F > 20_000_000:
+            B = max(1, 20_000_000 // F)
+        seed = int(rng.integers(0, 2 ** 32))
+        dt = ["f16", "f32", "bf16"][case % 3]
+        g_cpu = torch.randn(B, F, generator=torch.Generator().manual_seed(case)).to(DT[dt])
+        # the first rows are one-hot at boundary features
+        fts = o.feature_tile_size(F, T)
+        feats = sorted({0, F - 1, min(F - 1, fts), max(0, fts - 1), F // 2})[:B]
+        for i, f in enumerate(feats):
+            g_cpu[i].zero_()
+            g_cpu[i, f] = 1.0
+        g = g_cpu.to(cuda)
+        rad = ours(g, N, seed, T, RAD).cpu().numpy()
+        assert np.array_equal(rad[:len(feats)], o.matrix_rows(RAD, F, N, seed, T, feats)), (case, T, F, N, B, dt)
+        if B * F * N <= 3e11:
+            ref = o.project(RAD, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
+            assert rel_rows(rad, ref) <= TOL, (case, T, F, N, B, dt)
+            if dt != "bf16":
+                nor = ours(g, N, seed, T, NOR).cpu().numpy()
+                refn = o.project(NOR, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
+                assert rel_rows(nor, refn) <= TOL, (case, T, F, N, B, dt)
+
+
 def test_large_feature_count_and_projection_dim(cuda):
     """A shape from the reference's overflow tests (tests/test_jl.py:59-73: F = 180,645,096, k = 15,360):
     64-bit addressing in the restaging pass and matrix rows deep inside long feature tiles."""
