@@ -46,7 +46,7 @@ BLOCK = 100  # BasicProjector's column block (trak/projectors.py:229)
 # DRAM traffic of one projection-kernel launch on the full workload, from the ncu
 # capture summarised in profiles/project_kernel_normal_small.md (dram__bytes_read.sum +
 # dram__bytes_write.sum at D/10, which grows in proportion to D, times 10)
-NCU_TRAFFIC_BYTES_FULL = 3.53e9
+NCU_TRAFFIC_BYTES_FULL = 3.51e9
 
 
 def measured_peaks():
@@ -433,7 +433,7 @@ def run_ours(args, D):
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_FULL * D / D_FULL,
                          "kernel": f"project_kernel<{args.proj_type}>", "kernel_ms": kernel_ms,
                          "algorithmic_flop_per_launch": flop, "peak_source": peak_note,
-                         "note": ("generator-issue-bound: the Gaussian matrix costs ~550 instructions per "
+                         "note": ("generator-issue-bound: the Gaussian matrix costs ~530 instructions per "
                                   "16x32 tile, so the tensor pipe idles; see DESIGN.md") if ptype == _lib.TB_NORMAL
                          else "MMA-bound under the power cap plus the restaging pass; see DESIGN.md"},
             "e2e": {"value": e2e_value, "unit": "examples/s", "h2d_bytes_per_step": ROWS * D * 2,
