@@ -344,6 +344,19 @@ def test_bounded_wait_times_out_and_device_stays_usable(cuda):
     assert np.all(np.mod(fast_jl.project_rademacher_8(g, 512, 0, 148).cpu().numpy(), 2) == 0)
 
 
+def test_generator_square_root_is_exact_on_every_possible_draw(cuda):
+    """The Gaussian generator's shortened square root against sqrtf on all 2^32 draws (bit for bit)."""
+    from trak_b200 import _lib
+    lib = _lib.lib()
+    bad = torch.zeros(1, dtype=torch.int64, device=cuda)
+    total = 0
+    for first in range(0, 1 << 32, 1 << 30):
+        assert lib.tb_selftest_sqrt(cuda.index, None, first, 1 << 30, bad.data_ptr()) == 0
+        torch.cuda.synchronize()
+        total += int(bad.item())
+    assert total == 0, f"{total} draws give a different square root"
+
+
 def test_device_status_clean(cuda):
     from trak_b200 import _lib
     _lib.device_status(cuda.index)

@@ -37,6 +37,7 @@ SIGNATURES = {
     "tb_last_cuda_error": (ctypes.c_char_p, []),
     "tb_device_status": (_i, [_i, ctypes.POINTER(_u32)]),
     "tb_selftest_wait_timeout": (_i, [_i, _vp, _u32]),
+    "tb_selftest_sqrt": (_i, [_i, _vp, ctypes.c_uint64, ctypes.c_uint64, _vp]),
     "tb_project_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32]),
     "tb_profile_events": (_i, [_vp, _vp]),
     "tb_project_segments_workspace_bytes": (_sz, [_i, _i64, _i64, _u32, _u32, _i32]),
