@@ -177,10 +177,11 @@ int tb_project_static(int device, void *stream, const void *grads, int dtype, in
                       uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate);
 
 /* Exhaustive self-test of the Gaussian generator's square root (no counterpart in the reference).
- * The generator computes sqrtf(-2 logf(u)) with a shortened correctly rounded sequence that is only
- * valid on the values that expression can take.  This entry point evaluates both that sequence and
- * sqrtf for the draws first .. first + count - 1 (within [0, 2^32)) and writes the number of draws on
- * which they differ in any bit to *mismatches_dev (device memory, 8 bytes).  Zero over the whole
+ * The generator computes sqrtf(-2 logf(u)) with logf told its argument range and a shortened correctly
+ * rounded square root that is only valid on the values that expression can take.  This entry point
+ * evaluates both that and the plain sqrtf(-2 logf(u)) for the draws first .. first + count - 1 (within
+ * [0, 2^32)) and writes the number of draws on which they differ in any bit to *mismatches_dev (device
+ * memory, 8 bytes).  Zero over the whole
  * 32-bit range is what keeps the matrix bit-identical to the reference's. */
 int tb_selftest_sqrt(int device, void *stream, uint64_t first, uint64_t count, uint64_t *mismatches_dev);
 
