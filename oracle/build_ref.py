@@ -4,13 +4,18 @@ TEST INFRASTRUCTURE ONLY.  Nothing in the product package imports this.
 
 The reference kernel (``fast_jl/fast_jl.cu`` and the ``.cuh`` headers next to
 it) is compiled *where it lies* in the reference checkout, with one explicit
-``nvcc`` command (the reference's ``setup.py`` is not run), and the only
-output is ``oracle/_ref/fast_jl.so``.  No reference source is copied.
+``nvcc`` command (the reference's ``setup.py`` is not run), and its only
+output is ``oracle/_ref/fast_jl.so``.  No reference source is copied into
+tracked files.
 
 The resulting module is the bit-exactness witness for the projection matrix:
 GPU tests project one-hot rows through it and through the new kernel and
 compare the bits, and ``tests/golden/make_fastjl_golden.py`` uses it to
 produce the committed golden vectors.
+
+``install_python_package`` is the second recipe: the reference's pure-Python
+package, installed by pip into the git-ignored ``baseline/_ref``, which lets one
+GPU test run the unmodified ``TRAKer`` on top of this library.
 
 Usage:  python oracle/build_ref.py [--reference /path/to/reference]
 """
@@ -58,6 +63,24 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
     return OUT
 
 
+PY_DIR = os.path.join(os.path.dirname(HERE), "baseline", "_ref")
+
+
+def install_python_package(reference: str = "/root/reference", force: bool = False) -> str | None:
+    """Install the reference's pure-Python package (``trak``) with pip, offline and without
+    dependencies, into the git-ignored ``baseline/_ref`` directory, so that a GPU test can drive
+    this library through the unmodified ``TRAKer``.  Returns the directory, or None when neither
+    the checkout nor an earlier install is there."""
+    done = os.path.isdir(os.path.join(PY_DIR, "trak"))
+    if not os.path.exists(os.path.join(reference, "setup.py")) or (done and not force):
+        return PY_DIR if done else None
+    cmd = [sys.executable, "-m", "pip", "install", "--quiet", "--no-index", "--no-build-isolation", "--no-deps",
+           "--upgrade", "--target", PY_DIR, reference]
+    print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return PY_DIR
+
+
 def load():
     """Import the built witness as module ``fast_jl`` (None when not built)."""
     if not os.path.exists(OUT):
@@ -77,4 +100,6 @@ if __name__ == "__main__":
     a = ap.parse_args()
     p = build(a.reference, a.force)
     print("built:" if p else "reference not present; nothing built", p)
+    q = install_python_package(a.reference, a.force)
+    print("python package:" if q else "reference not present; nothing installed", q)
     sys.exit(0)

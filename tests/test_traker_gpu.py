@@ -1,0 +1,106 @@
+"""The reference's own, unmodified ``TRAKer`` driving this library end to end
+(trak/traker.py: featurize -> finalize_features -> start_scoring_checkpoint -> score ->
+finalize_scores), two ways:
+
+  A. nothing passed in: ``TRAKer`` imports ``fast_jl`` itself (trak/traker.py:254-262) and finds the
+     shim module registered under that name, builds the reference's ``CudaProjector`` on it, and scores
+     with the reference's ``BasicScoreComputer`` (torch on the GPU);
+  B. ``projector=`` this library's ``CudaProjector`` and ``score_computer=`` ``B200ScoreComputer``.
+
+Both must give the same attribution scores within 1e-3 (Frobenius-relative), and A's projected
+gradients must equal the CPU oracle's projection of the same per-sample gradients.
+
+The reference package is not part of this repository; ``__graft_entry__.build()`` installs it, where
+its checkout exists, into the git-ignored ``baseline/_ref`` directory, and the test is skipped when
+that directory is absent.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+_REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+
+
+@pytest.fixture()
+def trak(cuda, monkeypatch):
+    if not os.path.isdir(os.path.join(_REF, "trak")):
+        pytest.skip("reference package not installed under baseline/_ref")
+    import trak_b200.fast_jl as shim
+    monkeypatch.setitem(sys.modules, "fast_jl", shim)
+    monkeypatch.syspath_prepend(_REF)
+    for name in [m for m in sys.modules if m == "trak" or m.startswith("trak.")]:
+        monkeypatch.delitem(sys.modules, name)
+    import trak
+    assert os.path.abspath(trak.__file__).startswith(_REF)
+    return trak
+
+
+def _model_and_data(cuda):
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(
+        torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.ReLU(), torch.nn.AvgPool2d(2),
+        torch.nn.Flatten(), torch.nn.Linear(8 * 4 * 4, 32), torch.nn.ReLU(), torch.nn.Linear(32, 10),
+    ).to(cuda).eval()
+    g = torch.Generator().manual_seed(1)
+    n, m = 1200, 48
+    train = (torch.rand(n, 3, 8, 8, generator=g).to(cuda), torch.randint(0, 10, (n,), generator=g).to(cuda))
+    targets = (torch.rand(m, 3, 8, 8, generator=g).to(cuda), torch.randint(0, 10, (m,), generator=g).to(cuda))
+    return model, train, targets
+
+
+def _run(trak, model, train, targets, save_dir, **kw):
+    n, m = train[0].shape[0], targets[0].shape[0]
+    tr = trak.TRAKer(model=model, task="image_classification", train_set_size=n, save_dir=str(save_dir),
+                     device="cuda", proj_dim=1024, use_half_precision=False, lambda_reg=0.0,
+                     logging_level=40, **kw)
+    ckpt = model.state_dict()
+    tr.load_checkpoint(ckpt, model_id=0)
+    for i in range(0, n, 200):
+        tr.featurize(batch=(train[0][i:i + 200], train[1][i:i + 200]), num_samples=min(200, n - i))
+    # ridge term = a tenth of the Gram's mean eigenvalue (gradients of a tiny model have a fast-decaying
+    # spectrum), so that the comparison measures the kernels and not round-off amplified by the conditioning
+    X = np.array(tr.saver.current_store["grads"], dtype=np.float64)
+    tr.score_computer.lambda_reg = 0.1 * float((X ** 2).sum() / X.shape[1])
+    tr.finalize_features()
+    tr.start_scoring_checkpoint(exp_name="t", checkpoint=ckpt, model_id=0, num_targets=m)
+    tr.score(batch=targets, num_samples=m)
+    scores = np.array(tr.finalize_scores(exp_name="t"))
+    grads = np.array(tr.saver.current_store["grads"])
+    return tr, scores, grads
+
+
+def test_unmodified_traker_runs_on_the_shim_and_on_the_mirrored_classes(trak, cuda, tmp_path):
+    from oracle import jl_oracle as o
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    from trak_b200.score_computers import B200ScoreComputer
+    model, train, targets = _model_and_data(cuda)
+    D = sum(p.numel() for p in model.parameters())
+    tr_a, s_a, g_a = _run(trak, model, train, targets, tmp_path / "a")
+    assert type(tr_a.projector).__module__ == "trak.projectors"
+    assert type(tr_a.projector).__name__ == "CudaProjector"
+    assert type(tr_a.score_computer).__name__ == "BasicScoreComputer"
+
+    proj = CudaProjector(grad_dim=D, proj_dim=1024, seed=0, proj_type=ProjectionType.rademacher,
+                         device=cuda, max_batch_size=32)
+    tr_b, s_b, g_b = _run(trak, model, train, targets, tmp_path / "b",
+                          projector=proj, score_computer=B200ScoreComputer)
+    assert isinstance(tr_b.score_computer, B200ScoreComputer)
+
+    assert s_a.shape == s_b.shape == (train[0].shape[0], targets[0].shape[0])
+    assert np.isfinite(s_a).all() and np.abs(s_a).max() > 0
+    # same matrix, same gradients: the stored projections agree to fp32 summation order
+    assert np.linalg.norm(g_a - g_b) <= 1e-5 * np.linalg.norm(g_a)
+    err = np.linalg.norm(s_a - s_b) / np.linalg.norm(s_a)
+    assert err <= 1e-3, err
+
+    # A's stored projections against the CPU oracle on the same per-sample gradients
+    grads = tr_a.gradient_computer.compute_per_sample_grad(batch=(train[0][:64], train[1][:64]))
+    flat = trak.utils.vectorize(grads, device="cuda").float().cpu().numpy()
+    ref = o.project(o.RADEMACHER, flat, 1024, 0, tr_a.projector.num_sms, round_f16=True) / D ** 0.5
+    rel = np.linalg.norm(g_a[:64] - ref, axis=1) / np.linalg.norm(ref, axis=1)
+    assert rel.max() <= 1e-3, rel.max()
