@@ -125,3 +125,65 @@ def test_larger_shape_properties(cuda):
     inv = sc.spd_inverse_(g.clone(), 1e-3, rescale=False)
     eye = (g.double() + 1e-3 * torch.eye(k, device=cuda, dtype=torch.float64)) @ inv.double()
     assert float((eye - torch.eye(k, device=cuda, dtype=torch.float64)).abs().max()) < 1e-3
+
+
+def test_fp32_products_are_fp32_grade(cuda):
+    """fp32 operands travel as two fp16 planes of the row-scaled value (22-23 mantissa bits, the lo*lo term
+    dropped), and the row scales must absorb any spread of magnitudes between rows.  The Gram, whose error
+    the inverse amplifies, is accumulated 64 k at a time and must sit within a small factor of plain fp32
+    arithmetic; the other products keep one long tensor-core accumulation (truncating: about 1e-5)."""
+    from trak_b200 import score_computers as sc
+    g = torch.Generator(device=cuda).manual_seed(5)
+    a = torch.randn(700, 3000, device=cuda, generator=g)
+    b = torch.randn(900, 3000, device=cuda, generator=g)
+    exact = a.double() @ b.double().T
+    assert rel(sc.gemm_nt(a, b), exact) <= 3e-5
+    x = torch.randn(5000, 600, device=cuda, generator=g)
+    exact_gram = x.double().T @ x.double()
+    err = rel(sc.gram(x), exact_gram)
+    print(f"Gram 5000 x 600: {err:.2e} (torch fp32 matmul: {rel(x.T @ x, exact_gram):.2e})")
+    assert err <= 5e-7, err
+    # rows spread over twenty orders of magnitude each (and some all-zero): row-wise relative error
+    sa = 10.0 ** (torch.rand(700, 1, device=cuda, generator=g) * 20 - 18)
+    sb = 10.0 ** (torch.rand(900, 1, device=cuda, generator=g) * 20 - 2)
+    a2, b2 = a * sa, b * sb
+    a2[17] = 0
+    b2[5] = 0
+    got = sc.gemm_nt(a2, b2).double()
+    want = a2.double() @ b2.double().T
+    assert torch.isfinite(got).all()
+    assert float(got[17].abs().max()) == 0.0 and float(got[:, 5].abs().max()) == 0.0
+    keep = torch.ones(700, dtype=torch.bool, device=cuda)
+    keep[17] = False
+    rows = (got - want).norm(dim=1)[keep] / want.norm(dim=1)[keep]
+    assert float(rows.max()) <= 3e-5
+    # columns of the transposed operand (the Gram's scales) spread as well
+    x2 = x * 10.0 ** (torch.rand(1, 600, device=cuda, generator=g) * 30 - 15)
+    g2 = sc.gram(x2).double()
+    w2 = x2.double().T @ x2.double()
+    d = w2.diagonal().sqrt()
+    assert float(((g2 - w2) / (d[:, None] * d[None, :])).abs().max()) <= 1e-6
+
+
+def test_ill_conditioned_gram_keeps_the_scores_accurate(cuda):
+    """Features with a fast-decaying spectrum (what real gradient features look like): the inverse amplifies
+    any error of the Gram by its condition number (here about 3000), so the products have to be fp32-grade
+    for the scores to stay within the 1e-3 bar."""
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m = 4000, 512, 64
+    g = torch.Generator().manual_seed(11)
+    u = torch.linalg.qr(torch.randn(n, k, generator=g, dtype=torch.float64))[0]
+    v = torch.linalg.qr(torch.randn(k, k, generator=g, dtype=torch.float64))[0]
+    sv = torch.logspace(0, -2, k, dtype=torch.float64)            # singular values 1 ... 1e-2
+    X = ((u * sv) @ v.T).float()
+    T = (torch.randn(m, k, generator=g, dtype=torch.float64) @ (v * sv) @ v.T).float()
+    lam = float(sv[-1] ** 2 * 2.5)                                 # cond(G + lam I) about 2900
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, CUDA_MAX_DIM_SIZE=1500, lambda_reg=lam)
+    feats = sc.get_x_xtx_inv(X, sc.get_xtx(X))
+    acc = torch.zeros(n, m)
+    sc.get_scores(feats, T, acc)
+    Xd, Td = X.double(), T.double()
+    inv = torch.linalg.inv(Xd.T @ Xd + lam * torch.eye(k, dtype=torch.float64))
+    inv /= inv.abs().mean()
+    err = rel(acc, Xd @ inv @ Td.T)
+    assert err <= 2e-4, err

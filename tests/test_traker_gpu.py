@@ -70,8 +70,15 @@ def _run(trak, model, train, targets, save_dir, **kw):
     tr.start_scoring_checkpoint(exp_name="t", checkpoint=ckpt, model_id=0, num_targets=m)
     tr.score(batch=targets, num_samples=m)
     scores = np.array(tr.finalize_scores(exp_name="t"))
-    grads = np.array(tr.saver.current_store["grads"])
-    return tr, scores, grads
+    store = tr.saver.current_store
+    grads = np.array(store["grads"])
+    # the same scoring arithmetic in fp64 on the host, from the projections this run stored
+    # (trak/score_computers.py:145-189, trak/traker.py:676-678)
+    X, T = grads.astype(np.float64), np.array(store["t_grads"], dtype=np.float64)
+    inv = np.linalg.inv(X.T @ X + tr.score_computer.lambda_reg * np.eye(X.shape[1]))
+    inv /= np.abs(inv).mean()
+    exact = (X @ inv @ T.T) * np.array(store["out_to_loss"], dtype=np.float64)
+    return tr, scores, grads, exact
 
 
 def test_unmodified_traker_runs_on_the_shim_and_on_the_mirrored_classes(trak, cuda, tmp_path):
@@ -80,14 +87,14 @@ def test_unmodified_traker_runs_on_the_shim_and_on_the_mirrored_classes(trak, cu
     from trak_b200.score_computers import B200ScoreComputer
     model, train, targets = _model_and_data(cuda)
     D = sum(p.numel() for p in model.parameters())
-    tr_a, s_a, g_a = _run(trak, model, train, targets, tmp_path / "a")
+    tr_a, s_a, g_a, x_a = _run(trak, model, train, targets, tmp_path / "a")
     assert type(tr_a.projector).__module__ == "trak.projectors"
     assert type(tr_a.projector).__name__ == "CudaProjector"
     assert type(tr_a.score_computer).__name__ == "BasicScoreComputer"
 
     proj = CudaProjector(grad_dim=D, proj_dim=1024, seed=0, proj_type=ProjectionType.rademacher,
                          device=cuda, max_batch_size=32)
-    tr_b, s_b, g_b = _run(trak, model, train, targets, tmp_path / "b",
+    tr_b, s_b, g_b, x_b = _run(trak, model, train, targets, tmp_path / "b",
                           projector=proj, score_computer=B200ScoreComputer)
     assert isinstance(tr_b.score_computer, B200ScoreComputer)
 
@@ -95,12 +102,18 @@ def test_unmodified_traker_runs_on_the_shim_and_on_the_mirrored_classes(trak, cu
     assert np.isfinite(s_a).all() and np.abs(s_a).max() > 0
     # same matrix, same gradients: the stored projections agree to fp32 summation order
     assert np.linalg.norm(g_a - g_b) <= 1e-5 * np.linalg.norm(g_a)
-    err = np.linalg.norm(s_a - s_b) / np.linalg.norm(s_a)
-    assert err <= 1e-3, err
+    err_a = np.linalg.norm(s_a - x_a) / np.linalg.norm(x_a)
+    err_b = np.linalg.norm(s_b - x_b) / np.linalg.norm(x_b)
+    err_ab = np.linalg.norm(s_a - s_b) / np.linalg.norm(s_a)
+    print(f"scores vs fp64: reference classes {err_a:.2e}, this library {err_b:.2e}; A vs B {err_ab:.2e}")
+    assert err_b <= 1e-3, (err_a, err_b, err_ab)
+    assert err_ab <= 2e-2, (err_a, err_b, err_ab)
 
-    # A's stored projections against the CPU oracle on the same per-sample gradients
-    grads = tr_a.gradient_computer.compute_per_sample_grad(batch=(train[0][:64], train[1][:64]))
+    # A's stored projections against the CPU oracle on the same per-sample gradients (the first batch as
+    # featurize saw it).  The kernel, like the reference's, rounds fp32 gradients to fp16 on the way in;
+    # examples whose gradients are tiny sit in fp16's subnormal range, where a last-bit difference of a
+    # recomputed gradient moves the rounded value, so the comparison is over the batch, not per row.
+    grads = tr_a.gradient_computer.compute_per_sample_grad(batch=(train[0][:200], train[1][:200]))
     flat = trak.utils.vectorize(grads, device="cuda").float().cpu().numpy()
     ref = o.project(o.RADEMACHER, flat, 1024, 0, tr_a.projector.num_sms, round_f16=True) / D ** 0.5
-    rel = np.linalg.norm(g_a[:64] - ref, axis=1) / np.linalg.norm(ref, axis=1)
-    assert rel.max() <= 1e-3, rel.max()
+    assert np.linalg.norm(g_a[:200] - ref) <= 1e-3 * np.linalg.norm(ref)

@@ -4,11 +4,19 @@
 // (trak/score_computers.py:145-189):  X^T X  (A = B = X^T, symmetric mode),
 // X . inv  (inv is symmetric, so it is its own transpose) and  features . targets^T.
 //
-// fp32 inputs are not rounded to one tensor-core format.  A packing pass splits every
-// value into bf16 hi + bf16 lo (hi = rn(x), lo = rn(x - hi); together 16 mantissa bits)
-// and the kernel accumulates  hi*hi + hi*lo + lo*hi  in fp32 -- three MMAs per k-step at
-// the bf16 rate, about 1e-5 relative error where one TF32 pass gives about 5e-4.  fp16 and
-// bf16 inputs are exact in one plane and take one MMA per k-step.
+// fp32 inputs are not rounded to one tensor-core format.  A packing pass scales every
+// operand row by a power of two that brings its largest magnitude into [2^14, 2^15) and
+// splits the scaled value into fp16 hi + fp16 lo (hi = rn(x), lo = rn(x - hi); together 22
+// to 23 mantissa bits for every element within 2^-18 of its row's maximum, an absolute
+// floor of 2^-40 of that maximum below), and the kernel accumulates  hi*hi + hi*lo + lo*hi
+// in fp32 -- three MMAs per k-step at the 16-bit rate; the epilogue multiplies the two
+// inverse scales back in (powers of two: exact).  The dropped lo*lo term is below 2^-22
+// relative, so the products are within a small factor of plain fp32 arithmetic.  This
+// matters after the products: the regularised inverse amplifies a relative error of the
+// Gram by its condition number, and with bf16 planes (16 mantissa bits, 4e-6 per product)
+// a condition number of 1000 already cost 3e-3 in the scores.  The scale needs one more
+// read of the operand (row maxima) before the packing pass.  fp16 and bf16 inputs are
+// exact in one plane and take one MMA per k-step, unscaled.
 //
 // The packing pass also tiles the operands the way the pipeline consumes them:
 // [128-row block][32-wide k block][plane][128 rows][32 k], so every TMA box is one
@@ -34,6 +42,8 @@ constexpr uint32_t GTILE_BYTES = 128 * GK * 2;  // one [128 x 32] 16-bit tile: 8
 struct GemmParams {
     float* C;
     const float* row_scale;  // nullable, length M
+    const uint32_t* amax_a;  // fp32 inputs: bit pattern of max |.| of every packed row of A (else null)
+    const uint32_t* amax_b;  // the same for B
     uint32_t* status;
     int64_t ldc;
     uint32_t M, N;
@@ -50,6 +60,20 @@ struct GemmParams {
 __device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) |
            (4ull << 61);
+}
+
+// Power-of-two scale of a packed fp32 operand row whose largest magnitude has the bit pattern
+// `amax_bits`: the biased exponent E is clamped to [16, 254] so that both 2^(141 - E) (brings
+// the maximum into [2^14, 2^15), inside fp16's range) and its inverse are normal numbers.
+__device__ __forceinline__ uint32_t scale_exponent(uint32_t amax_bits) {
+    const uint32_t e = amax_bits >> 23;
+    return e < 16u ? 16u : (e > 254u ? 254u : e);
+}
+__device__ __forceinline__ float row_scale_up(uint32_t amax_bits) {
+    return __uint_as_float((268u - scale_exponent(amax_bits)) << 23);
+}
+__device__ __forceinline__ float row_scale_down(uint32_t amax_bits) {
+    return __uint_as_float((scale_exponent(amax_bits) - 14u) << 23);
 }
 
 __device__ __forceinline__ void gemm_fail(uint32_t* status, volatile uint32_t* abort_flag, uint32_t code,
@@ -74,6 +98,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ uint64_t bar_acc;
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_word;
+    __shared__ float col_factor[256];  // inverse scale of every column of this tile (1 when unscaled)
     volatile uint32_t* abort_flag = &abort_word;
 
     // Tile order: CTAs are numbered so that the ~148 that run together cover a block of about
@@ -179,6 +204,11 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp >= 4) {
         // --------------------------------- epilogue ---------------------------------
         const uint32_t q = warp & 3u, chalf = (warp - 4u) >> 2;  // TMEM lane quarter, column half
+        {
+            const uint32_t t = threadIdx.x - 128u, n = tile_n * 256u + t;
+            col_factor[t] = (p.amax_b && n < p.N) ? row_scale_down(p.amax_b[n]) : 1.0f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps only
+        }
         bool got = mbar_wait(smem_u32(&bar_acc), 0u, abort_flag);
         got = __all_sync(0xffffffffu, got);
         if (!got) {
@@ -193,6 +223,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (uint32_t mb = 0; mb < 2; ++mb) {
                 const uint32_t m = tile_m * 256u + mb * 128u + q * 32u + lane;
                 const float rs = p.alpha * ((p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f);
+                const float fa = (p.amax_a && m < p.M) ? row_scale_down(p.amax_a[m]) : 1.0f;
 #pragma unroll 1
                 for (uint32_t cb = 0; cb < 8; ++cb) {
                     const uint32_t c0 = chalf * 128u + cb * 16u;
@@ -200,12 +231,16 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld_x16(tmem_base + lane_base + mb * 256u + c0, r);
                     tmem_wait_ld();
                     const uint32_t n0 = tile_n * 256u + c0;
+                    float val[16];  // one value per entry: the mirrored store writes the same bits
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        val[j] = ((__uint_as_float(r[j]) * fa) * col_factor[c0 + j]) * rs;
                     if (m < p.M) {
                         float* dst = p.C + (int64_t)m * p.ldc + n0;
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             if (n0 + j < p.N && (!sym || n0 + j >= m)) {
-                                float v = rs * __uint_as_float(r[j]);
+                                float v = val[j];
                                 if (p.accumulate) v += dst[j];
                                 dst[j] = v;
                             }
@@ -217,7 +252,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < 16; ++j) {
                             if (n0 + j < p.M && n0 + j > m) {
                                 float* dst = p.C + (int64_t)(n0 + j) * p.ldc + m;
-                                float v = p.alpha * __uint_as_float(r[j]);
+                                float v = val[j];
                                 if (p.accumulate) v += *dst;
                                 *dst = v;
                             }
@@ -237,14 +272,263 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- chunked accumulation: the variant for products whose error gets amplified ---------------
+// The tensor core adds into its fp32 accumulator by truncation, not rounding: every MMA whose
+// addends reach below the accumulator's last place pulls the sum towards zero by up to one unit
+// in the last place, and a K-long contraction is a chain of 3K/16 such steps (measured: 1e-5
+// relative at K = 3000, 2e-3 in the scores once a Gram with condition number 1000 is inverted,
+// where plain fp32 arithmetic gives 3e-5).  Here the chain is cut every 64 k: one CTA owns a
+// 128 x 256 tile, TMEM holds two accumulator sets, the MMA warp fills one set with a 64-wide
+// chunk -- first the hi*lo and lo*hi terms (small, so their truncation is 2^-11 smaller), then
+// the four hi*hi MMAs -- while the eight epilogue warps read the other set and add it, with
+// ordinary rounded fp32 adds, to running sums they keep in registers (128 per thread).
+constexpr uint32_t CK_SLOTS = 4;
+constexpr uint32_t CK_SLOT_BYTES = 6 * GTILE_BYTES;  // A: hi, lo; B: [plane][two row blocks]  (48 KB per 32 k)
+
+__global__ void __launch_bounds__(384, 1)
+gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[CK_SLOTS];
+    __shared__ uint64_t bar_empty[CK_SLOTS];
+    __shared__ uint64_t bar_acc_full[2];
+    __shared__ uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_word;
+    __shared__ float col_factor[256];
+    volatile uint32_t* abort_flag = &abort_word;
+
+    // same L2-friendly numbering as gemm_nt_kernel, with 128-row tiles
+    constexpr uint32_t GROUP_M = 16;
+    const uint32_t tiles_n = gridDim.x, tiles_m = gridDim.y;
+    const uint32_t id = blockIdx.y * tiles_n + blockIdx.x;
+    const uint32_t width = GROUP_M * tiles_n;
+    const uint32_t first_m = (id / width) * GROUP_M;
+    const uint32_t gsize = min(tiles_m - first_m, GROUP_M);
+    const uint32_t tile_m = first_m + (id % width) % gsize, tile_n = (id % width) / gsize;
+    // symmetric: a tile is needed when it holds some entry with n >= m
+    if (p.symmetric && tile_n < (tile_m >> 1)) return;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t nchunks = (p.kblocks + 1u) >> 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < CK_SLOTS; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bar_acc_full[s]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[s]), 8);  // one arrival per epilogue warp
+        }
+        abort_word = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        prefetch_tmap(&map_a);
+        prefetch_tmap(&map_b);
+        uint32_t slot = 0, ph = 0;
+        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+            if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) {
+                gemm_fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, kb);
+                break;
+            }
+            const uint32_t bar = smem_u32(&bar_full[slot]);
+            const uint32_t sa = smem_base + slot * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+            mbar_expect_tx(bar, CK_SLOT_BYTES);
+#pragma unroll
+            for (uint32_t pl = 0; pl < 2; ++pl) {
+                tma_load_2d(sa + pl * GTILE_BYTES, &map_a, 0, (int)(((tile_m * p.kblocks + kb) * 2u + pl) * 128u), bar);
+#pragma unroll
+                for (uint32_t h = 0; h < 2; ++h)
+                    tma_load_2d(sb + (pl * 2u + h) * GTILE_BYTES, &map_b, 0,
+                                (int)((((tile_n * 2u + h) * p.kblocks + kb) * 2u + pl) * 128u), bar);
+            }
+            if (++slot == CK_SLOTS) {
+                slot = 0;
+                ph ^= 1u;
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // -------------------------------- MMA issuer --------------------------------
+        uint32_t slot = 0, ph = 0;  // a chunk takes slots (slot, slot + 1); slot stays even, so no wrap inside one
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t set = c & 1u, use = c >> 1;
+            if (!mbar_wait(smem_u32(&bar_acc_empty[set]), (use & 1u) ^ 1u, abort_flag)) {
+                gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x10000u + c);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d = tmem_base + set * 256u;
+            const uint32_t nkb = min(2u, p.kblocks - 2u * c);
+            bool ok = true;
+            // the small terms of the whole chunk first ...
+            for (uint32_t j = 0; j < nkb && ok; ++j) {
+                if (!mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag)) {
+                    gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, 2u * c + j);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+#pragma unroll
+                for (uint32_t kk = 0; kk < 2; ++kk) {
+                    const uint64_t a_hi = smem_desc_k_sw64(sa) + 2u * kk;
+                    const uint64_t a_lo = smem_desc_k_sw64(sa + GTILE_BYTES) + 2u * kk;
+                    const uint64_t b_hi = smem_desc_k_sw64(sb) + 2u * kk;
+                    const uint64_t b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES) + 2u * kk;
+                    umma_f16_ss(d, a_hi, b_lo, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_f16_ss(d, a_lo, b_hi, p.idesc, 1u);
+                }
+            }
+            if (!ok) break;
+            // ... then the large ones, releasing each slot as its last MMA is queued
+            for (uint32_t j = 0; j < nkb; ++j) {
+                const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+#pragma unroll
+                for (uint32_t kk = 0; kk < 2; ++kk)
+                    umma_f16_ss(d, smem_desc_k_sw64(sa) + 2u * kk, smem_desc_k_sw64(sb) + 2u * kk, p.idesc, 1u);
+                tc_commit(smem_u32(&bar_empty[slot + j]));
+            }
+            tc_commit(smem_u32(&bar_acc_full[set]));
+            slot += nkb;
+            if (slot >= CK_SLOTS) {
+                slot = 0;
+                ph ^= 1u;
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------------- running sums, then the epilogue ----------------------
+        const uint32_t q = warp & 3u, chalf = (warp - 4u) >> 2;  // TMEM lane quarter, column half
+        {
+            const uint32_t t = threadIdx.x - 128u, n = tile_n * 256u + t;
+            col_factor[t] = (p.amax_b && n < p.N) ? row_scale_down(p.amax_b[n]) : 1.0f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps only
+        }
+        const uint32_t lane_base = (q * 32u) << 16;
+        float sum[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) sum[i] = 0.0f;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t set = c & 1u, use = c >> 1;
+            bool got = mbar_wait(smem_u32(&bar_acc_full[set]), use & 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+                if (lane == 0) gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, c);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + lane_base + set * 256u + chalf * 128u;
+#pragma unroll
+            for (uint32_t cb = 0; cb < 8; ++cb) {
+                uint32_t r[16];
+                tmem_ld_x16(t0 + cb * 16u, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sum[cb * 16 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[set]));
+        }
+        if (ok) {
+            const bool sym = p.symmetric != 0;
+            const uint32_t m = tile_m * 128u + q * 32u + lane;
+            const uint32_t n0 = tile_n * 256u + chalf * 128u;
+            const float rs = p.alpha * ((p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f);
+            const float fa = (p.amax_a && m < p.M) ? row_scale_down(p.amax_a[m]) : 1.0f;
+#pragma unroll
+            for (int i = 0; i < 128; ++i) sum[i] = ((sum[i] * fa) * col_factor[chalf * 128u + i]) * rs;
+            if (m < p.M) {
+                float* dst = p.C + (int64_t)m * p.ldc + n0;
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (n0 + i < p.N && (!sym || n0 + i >= m)) {
+                        float v = sum[i];
+                        if (p.accumulate) v += dst[i];
+                        dst[i] = v;
+                    }
+                }
+            }
+            if (sym && m < p.N) {
+                // C[n, m] gets the same bits: for a fixed i the warp's lanes hold consecutive m
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (n0 + i < p.M && n0 + i > m) {
+                        float* dst = p.C + (int64_t)(n0 + i) * p.ldc + m;
+                        float v = sum[i];
+                        if (p.accumulate) v += *dst;
+                        *dst = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) __nanosleep(200000);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- row maxima of fp32 operands (the scales of the packing pass) -------------------------
+// amax[R] = bit pattern of max_k |operand[R][k]|  (non-negative floats order like their bits).
+// Operand rows are source rows: one warp per row, lanes along k.
+__global__ void amax_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ amax, uint64_t rows,
+                                 uint64_t K, uint64_t ld) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t R = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; R < rows; R += warps) {
+        const uint32_t* row = reinterpret_cast<const uint32_t*>(src + R * ld);
+        uint32_t m = 0;
+#pragma unroll 8
+        for (uint64_t k = lane; k < K; k += 32u) m = max(m, row[k] & 0x7fffffffu);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) amax[R] = m;
+    }
+}
+// Operand rows are source columns (the operand is the transpose): threads along the columns,
+// blockIdx.y walks chunks of source rows; amax must be zero before the launch.
+__global__ void amax_cols_kernel(const float* __restrict__ src, uint32_t* __restrict__ amax, uint64_t rows,
+                                 uint64_t K, uint64_t ld, uint64_t chunk) {
+    const uint64_t R = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (R >= rows) return;
+    const uint64_t k0 = (uint64_t)blockIdx.y * chunk, k1 = min(K, k0 + chunk);
+    const uint32_t* col = reinterpret_cast<const uint32_t*>(src) + R;
+    uint32_t m = 0;
+#pragma unroll 8
+    for (uint64_t k = k0; k < k1; ++k) m = max(m, col[k * ld] & 0x7fffffffu);
+    atomicMax(&amax[R], m);
+}
+
 // ---- packing ---------------------------------------------------------------------------
 // packed[((rb*kblocks + kb)*NPL + pl)*128 + r][kk]  (16-bit), r < 128, kk < 32:
 //   operand row  R = rb*128 + r,  k = kb*32 + kk;
 //   value = src[R*ld + k]  (TRANS = false)  or  src[k*ld + R]  (TRANS = true: the operand is the
 //   transpose of the row-major source), zero outside [rows x K].
-// In: float (NPL = 2: bf16 hi / lo planes) or a 16-bit type copied as is (NPL = 1).
+// In: float (NPL = 2: the value times its row's power-of-two scale, as fp16 hi / lo planes) or a
+// 16-bit type copied as is (NPL = 1).
 template <typename In, int NPL, bool TRANS>
-__global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ packed, uint64_t rows,
+__global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ packed,
+                            const uint32_t* __restrict__ amax, uint64_t rows,
                             uint64_t K, uint64_t ld, uint32_t rowblocks, uint32_t kblocks) {
     // one thread = 8 consecutive k of one operand row (a 16-byte store per plane)
     const uint64_t total = (uint64_t)rowblocks * kblocks * 128u * 4u;
@@ -264,6 +548,8 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
         const uint64_t rb = rest / kblocks;
         const uint64_t R = rb * 128u + r, k0 = (uint64_t)kb * 32u + oct * 8u;
         uint16_t hi[8], lo[8];
+        float up = 1.0f;
+        if constexpr (sizeof(In) == 4) up = R < rows ? row_scale_up(amax[R]) : 1.0f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             hi[e] = 0;
@@ -271,10 +557,11 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
             if (R < rows && k0 + e < K) {
                 const In x = TRANS ? src[(k0 + e) * ld + R] : src[R * ld + k0 + e];
                 if constexpr (sizeof(In) == 4) {
-                    const __nv_bfloat16 h = __float2bfloat16_rn(x);
-                    const __nv_bfloat16 l = __float2bfloat16_rn(x - __bfloat162float(h));
-                    hi[e] = *reinterpret_cast<const uint16_t*>(&h);
-                    lo[e] = *reinterpret_cast<const uint16_t*>(&l);
+                    const float xs = x * up;  // exact: a power of two, |xs| < 2^15
+                    const __half h = __float2half_rn(xs);
+                    const __half l = __float2half_rn(xs - __half2float(h));  // the difference is exact
+                    hi[e] = __half_as_ushort(h);
+                    lo[e] = __half_as_ushort(l);
                 } else {
                     hi[e] = *reinterpret_cast<const uint16_t*>(&x);
                 }
@@ -303,7 +590,9 @@ Packed packed_geometry(int dtype, int64_t rows, int64_t K) {
     g.rowblocks = (uint32_t)((rows + 127) / 128);
     g.kblocks = (uint32_t)((K + 31) / 32);
     g.npl = dtype == TB_F32 ? 2u : 1u;
-    g.bytes = align_up((size_t)g.rowblocks * g.kblocks * g.npl * GTILE_BYTES, 1024);
+    g.data_bytes = align_up((size_t)g.rowblocks * g.kblocks * g.npl * GTILE_BYTES, 1024);
+    // fp32 operands carry the row maxima behind the tiles
+    g.bytes = g.data_bytes + (dtype == TB_F32 ? align_up((size_t)g.rowblocks * 128u * sizeof(uint32_t), 1024) : 0);
     return g;
 }
 
@@ -316,16 +605,28 @@ int launch_pack(const void* src, int dtype, bool trans, uint64_t rows, uint64_t 
     const uint32_t nb = (uint32_t)blocks;
     if (dtype == TB_F32) {
         const float* s = static_cast<const float*>(src);
-        if (trans)
-            pack_kernel<float, 2, true><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
-        else
-            pack_kernel<float, 2, false><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+        uint32_t* amax = packed_amax(packed, g);
+        if (trans) {
+            TB_CUDA(cudaMemsetAsync(amax, 0, (size_t)g.rowblocks * 128u * sizeof(uint32_t), stream));
+            const uint32_t bx = (uint32_t)((rows + 255) / 256);
+            uint64_t by = ((uint64_t)sm_count * 16 + bx - 1) / bx;  // about 16 CTAs per SM in all
+            if (by > (K + 63) / 64) by = (K + 63) / 64;
+            if (by > 65535) by = 65535;
+            const uint64_t chunk = (K + by - 1) / by;
+            amax_cols_kernel<<<dim3(bx, (uint32_t)((K + chunk - 1) / chunk)), 256, 0, stream>>>(s, amax, rows, K, ld, chunk);
+            pack_kernel<float, 2, true><<<nb, 256, 0, stream>>>(s, packed, amax, rows, K, ld, g.rowblocks, g.kblocks);
+        } else {
+            uint64_t ab = (rows + 7) / 8;  // eight warps (rows) per CTA
+            if (ab > cap) ab = cap;
+            amax_rows_kernel<<<(uint32_t)ab, 256, 0, stream>>>(s, amax, rows, K, ld);
+            pack_kernel<float, 2, false><<<nb, 256, 0, stream>>>(s, packed, amax, rows, K, ld, g.rowblocks, g.kblocks);
+        }
     } else {
         const uint16_t* s = static_cast<const uint16_t*>(src);
         if (trans)
-            pack_kernel<uint16_t, 1, true><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+            pack_kernel<uint16_t, 1, true><<<nb, 256, 0, stream>>>(s, packed, nullptr, rows, K, ld, g.rowblocks, g.kblocks);
         else
-            pack_kernel<uint16_t, 1, false><<<nb, 256, 0, stream>>>(s, packed, rows, K, ld, g.rowblocks, g.kblocks);
+            pack_kernel<uint16_t, 1, false><<<nb, 256, 0, stream>>>(s, packed, nullptr, rows, K, ld, g.rowblocks, g.kblocks);
     }
     TB_CUDA(cudaGetLastError());
     return TB_OK;
@@ -335,14 +636,15 @@ static int packed_tmap(CUtensorMap* map, const uint16_t* packed, const Packed& g
     const uint64_t dims[2] = {GK, (uint64_t)g.rowblocks * g.kblocks * g.npl * 128u};
     const uint64_t strides[1] = {GK * 2u};
     const uint32_t box[2] = {GK, 128};
-    return encode_tmap(map, dtype == TB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+    return encode_tmap(map, dtype == TB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                        2, packed, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 // C[M x N] (+)= alpha * row_scale[m] * Apacked . Bpacked^T
 int launch_gemm(int device, cudaStream_t stream, const uint16_t* pa, const Packed& ga,
                        const uint16_t* pb, const Packed& gb, int dtype, int64_t M, int64_t N, float* C,
-                       int64_t ldc, const float* row_scale, float alpha, int accumulate, int symmetric) {
+                       int64_t ldc, const float* row_scale, float alpha, int accumulate, int symmetric,
+                       int chunked) {
     CUtensorMap map_a, map_b;
     int rc = packed_tmap(&map_a, pa, ga, dtype);
     if (rc != TB_OK) return rc;
@@ -351,15 +653,25 @@ int launch_gemm(int device, cudaStream_t stream, const uint16_t* pa, const Packe
     GemmParams p;
     p.C = C;
     p.row_scale = row_scale;
+    p.amax_a = dtype == TB_F32 ? packed_amax(pa, ga) : nullptr;
+    p.amax_b = dtype == TB_F32 ? packed_amax(pb, gb) : nullptr;
     p.status = status_ptr(device);
     p.ldc = ldc;
     p.M = (uint32_t)M;
     p.N = (uint32_t)N;
     p.kblocks = ga.kblocks;
-    p.idesc = idesc_f16(dtype == TB_F16 ? 0u : 1u, 256);
+    p.idesc = idesc_f16(dtype == TB_BF16 ? 1u : 0u, 256);  // fp32 operands travel as fp16 planes
     p.alpha = alpha;
     p.accumulate = accumulate;
     p.symmetric = symmetric;
+    if (chunked && ga.npl == 2) {
+        const size_t smem = (size_t)CK_SLOTS * CK_SLOT_BYTES + 1024u;
+        dim3 grid((uint32_t)((N + 255) / 256), (uint32_t)((M + 127) / 128), 1);
+        TB_CUDA(cudaFuncSetAttribute(gemm_nt_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        gemm_nt_chunked_kernel<<<grid, 384, smem, stream>>>(map_a, map_b, p);
+        TB_CUDA(cudaGetLastError());
+        return TB_OK;
+    }
     const uint32_t stage_bytes = 4u * ga.npl * GTILE_BYTES;
     p.stages = (200u * 1024u) / stage_bytes;
     if (p.stages > 8) p.stages = 8;
@@ -411,7 +723,7 @@ int tb_gemm_nt(int device, void* stream_, const void* A, int64_t lda, const void
     if (rc != TB_OK) return rc;
     rc = launch_pack(B, dtype, false, N, K, ldb, pb, gb, sm_count, stream);
     if (rc != TB_OK) return rc;
-    return launch_gemm(device, stream, pa, ga, pb, gb, dtype, M, N, C, ldc, row_scale, alpha, accumulate, 0);
+    return launch_gemm(device, stream, pa, ga, pb, gb, dtype, M, N, C, ldc, row_scale, alpha, accumulate, 0, 0);
 }
 
 size_t tb_gram_workspace_bytes(int dtype, int64_t n, int64_t k) {
@@ -437,7 +749,8 @@ int tb_gram(int device, void* stream_, const void* X, int dtype, int64_t n, int6
     uint16_t* px = static_cast<uint16_t*>(ws);
     rc = launch_pack(X, dtype, true, k, n, ld, px, g, sm_count, stream);
     if (rc != TB_OK) return rc;
-    return launch_gemm(device, stream, px, g, px, g, dtype, k, k, G, ldg, nullptr, 1.0f, accumulate, 1);
+    // the Gram feeds an inverse, which amplifies its error by the condition number: chunked accumulation
+    return launch_gemm(device, stream, px, g, px, g, dtype, k, k, G, ldg, nullptr, 1.0f, accumulate, 1, 1);
 }
 
 }  // extern "C"

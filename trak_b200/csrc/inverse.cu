@@ -359,7 +359,7 @@ int tb_spd_inverse(int device, void* stream_, float* A, int64_t k, int64_t lda, 
         const Packed g = packed_geometry(TB_F32, k, k);
         rc = launch_pack(A, TB_F32, true, (uint64_t)k, (uint64_t)k, (uint64_t)lda, packed, g, sm_count, stream);
         if (rc != TB_OK) return rc;
-        rc = launch_gemm(device, stream, packed, g, packed, g, TB_F32, k, k, A, lda, nullptr, 1.0f, 0, 1);
+        rc = launch_gemm(device, stream, packed, g, packed, g, TB_F32, k, k, A, lda, nullptr, 1.0f, 0, 1, 1);
         if (rc != TB_OK) return rc;
     }
 
