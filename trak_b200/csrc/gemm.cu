@@ -4,19 +4,27 @@
 // (trak/score_computers.py:145-189):  X^T X  (A = B = X^T, symmetric mode),
 // X . inv  (inv is symmetric, so it is its own transpose) and  features . targets^T.
 //
-// fp32 inputs are not rounded to one tensor-core format.  A packing pass scales every
-// operand row by a power of two that brings its largest magnitude into [2^14, 2^15) and
-// splits the scaled value into fp16 hi + fp16 lo (hi = rn(x), lo = rn(x - hi); together 22
-// to 23 mantissa bits for every element within 2^-18 of its row's maximum, an absolute
-// floor of 2^-40 of that maximum below), and the kernel accumulates  hi*hi + hi*lo + lo*hi
-// in fp32 -- three MMAs per k-step at the 16-bit rate; the epilogue multiplies the two
-// inverse scales back in (powers of two: exact).  The dropped lo*lo term is below 2^-22
-// relative, so the products are within a small factor of plain fp32 arithmetic.  This
-// matters after the products: the regularised inverse amplifies a relative error of the
-// Gram by its condition number, and with bf16 planes (16 mantissa bits, 4e-6 per product)
-// a condition number of 1000 already cost 3e-3 in the scores.  The scale needs one more
-// read of the operand (row maxima) before the packing pass.  fp16 and bf16 inputs are
-// exact in one plane and take one MMA per k-step, unscaled.
+// fp32 inputs are not rounded to one tensor-core format.  A packing pass scales every operand
+// row by the power of two that brings its largest magnitude into [2^14, 2^15) and splits the
+// scaled value into fp16 hi + fp16 lo (hi = rn(x), lo = rn(x - hi): 22 to 23 mantissa bits for
+// every element within 2^-18 of its row's maximum, an absolute floor of 2^-40 of that maximum
+// below), the kernels accumulate  hi*hi + hi*lo + lo*hi  in fp32 -- three MMAs per k-step at the
+// 16-bit rate, the dropped lo*lo term is under 2^-22 -- and the epilogue multiplies the two
+// inverse scales back in (powers of two: exact).  The scales cost one more read of the operand
+// (row maxima) before the packing pass.  What is left is the tensor core's own accumulation,
+// which truncates instead of rounding: every MMA whose addends reach below the accumulator's
+// last place pulls the sum towards zero, and a K-long contraction is a chain of 3K/16 such steps.
+//  * X . inv and features . targets^T (gemm_nt_kernel) keep one accumulation over all of K:
+//    about 1e-5 relative at K = 3000 ... 8192 (one TF32 pass would give 5e-4).  With bf16
+//    instead of fp16 planes (16 mantissa bits) these two products cost 2.5 times the error in
+//    the scores of an ill-conditioned problem and were 5 % faster.
+//  * X^T X and W^T W (gemm_nt_chunked_kernel) feed or form an inverse, which multiplies a
+//    relative error of the Gram by its condition number (measured: condition number 1000 turned
+//    the 1e-5 into 2e-3 in the scores where plain fp32 arithmetic gives 3e-5).  There the tensor
+//    core accumulates only 64 k at a time and the chunks are summed with rounded fp32 adds:
+//    within 2x of cuBLAS fp32 at n = 5000 and closer to the exact Gram than cuBLAS fp32 at
+//    n = 65,536 (5e-7 against 8e-6).
+// fp16 and bf16 inputs are exact in one plane and take one MMA per k-step, unscaled.
 //
 // The packing pass also tiles the operands the way the pipeline consumes them:
 // [128-row block][32-wide k block][plane][128 rows][32 k], so every TMA box is one
@@ -334,7 +342,13 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
 
-    if (warp == 0 && lane == 0) {
+    // Registers follow the work: the warpgroup of the two single-thread roles gives most of its
+    // allocation back (168 -> 56 per thread), the two epilogue warpgroups take it (168 -> 224:
+    // 128 running sums + 64 values in flight).  Each role's code sits wholly inside its branch,
+    // which is what lets the compiler allocate past the launch bound there.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (warp == 0 && lane == 0) {
         // ------------------------------- TMA producer -------------------------------
         prefetch_tmap(&map_a);
         prefetch_tmap(&map_b);
@@ -408,7 +422,9 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 ph ^= 1u;
             }
         }
-    } else if (warp >= 4) {
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------------- running sums, then the epilogue ----------------------
         const uint32_t q = warp & 3u, chalf = (warp - 4u) >> 2;  // TMEM lane quarter, column half
         {
@@ -434,12 +450,15 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tc_fence_after();
             const uint32_t t0 = tmem_base + lane_base + set * 256u + chalf * 128u;
 #pragma unroll
-            for (uint32_t cb = 0; cb < 8; ++cb) {
-                uint32_t r[16];
-                tmem_ld_x16(t0 + cb * 16u, r);
+            for (uint32_t cb = 0; cb < 8; cb += 4) {  // four loads in flight per wait
+                uint32_t r[4][16];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) tmem_ld_x16(t0 + (cb + u) * 16u, r[u]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) sum[cb * 16 + j] += __uint_as_float(r[j]);
+                for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[(cb + u) * 16 + j] += __uint_as_float(r[u][j]);
             }
             tc_fence_before();
             __syncwarp();
@@ -544,8 +563,10 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
             r = (uint32_t)((i >> 2) & 127u);
         }
         rest = i >> 9;
-        const uint32_t kb = (uint32_t)(rest % kblocks);
-        const uint64_t rb = rest / kblocks;
+        // consecutive CTAs take neighbouring pieces of the same source rows: along k when the operand
+        // rows are source rows, along the operand rows when they are source columns
+        const uint32_t kb = TRANS ? (uint32_t)(rest / rowblocks) : (uint32_t)(rest % kblocks);
+        const uint64_t rb = TRANS ? rest % rowblocks : rest / kblocks;
         const uint64_t R = rb * 128u + r, k0 = (uint64_t)kb * 32u + oct * 8u;
         uint16_t hi[8], lo[8];
         float up = 1.0f;
@@ -587,12 +608,13 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
 // ---- host side -----------------------------------------------------------------------------
 Packed packed_geometry(int dtype, int64_t rows, int64_t K) {
     Packed g;
+    g.scaled = dtype == TB_F32;
     g.rowblocks = (uint32_t)((rows + 127) / 128);
     g.kblocks = (uint32_t)((K + 31) / 32);
     g.npl = dtype == TB_F32 ? 2u : 1u;
     g.data_bytes = align_up((size_t)g.rowblocks * g.kblocks * g.npl * GTILE_BYTES, 1024);
-    // fp32 operands carry the row maxima behind the tiles
-    g.bytes = g.data_bytes + (dtype == TB_F32 ? align_up((size_t)g.rowblocks * 128u * sizeof(uint32_t), 1024) : 0);
+    // scaled operands carry the row maxima behind the tiles
+    g.bytes = g.data_bytes + (g.scaled ? align_up((size_t)g.rowblocks * 128u * sizeof(uint32_t), 1024) : 0);
     return g;
 }
 
@@ -632,11 +654,14 @@ int launch_pack(const void* src, int dtype, bool trans, uint64_t rows, uint64_t 
     return TB_OK;
 }
 
+// element format of the planes: fp16 for fp16 inputs and for scaled fp32 operands, else bf16
+static bool planes_are_fp16(const Packed& g, int dtype) { return dtype == TB_F16 || g.scaled; }
+
 static int packed_tmap(CUtensorMap* map, const uint16_t* packed, const Packed& g, int dtype) {
     const uint64_t dims[2] = {GK, (uint64_t)g.rowblocks * g.kblocks * g.npl * 128u};
     const uint64_t strides[1] = {GK * 2u};
     const uint32_t box[2] = {GK, 128};
-    return encode_tmap(map, dtype == TB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+    return encode_tmap(map, planes_are_fp16(g, dtype) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                        2, packed, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
@@ -653,14 +678,15 @@ int launch_gemm(int device, cudaStream_t stream, const uint16_t* pa, const Packe
     GemmParams p;
     p.C = C;
     p.row_scale = row_scale;
-    p.amax_a = dtype == TB_F32 ? packed_amax(pa, ga) : nullptr;
-    p.amax_b = dtype == TB_F32 ? packed_amax(pb, gb) : nullptr;
+    if (ga.scaled != gb.scaled || (chunked && !ga.scaled)) return TB_ERR_BAD_ARG;
+    p.amax_a = ga.scaled ? packed_amax(pa, ga) : nullptr;
+    p.amax_b = gb.scaled ? packed_amax(pb, gb) : nullptr;
     p.status = status_ptr(device);
     p.ldc = ldc;
     p.M = (uint32_t)M;
     p.N = (uint32_t)N;
     p.kblocks = ga.kblocks;
-    p.idesc = idesc_f16(dtype == TB_BF16 ? 1u : 0u, 256);  // fp32 operands travel as fp16 planes
+    p.idesc = idesc_f16(planes_are_fp16(ga, dtype) ? 0u : 1u, 256);
     p.alpha = alpha;
     p.accumulate = accumulate;
     p.symmetric = symmetric;
@@ -750,7 +776,8 @@ int tb_gram(int device, void* stream_, const void* X, int dtype, int64_t n, int6
     rc = launch_pack(X, dtype, true, k, n, ld, px, g, sm_count, stream);
     if (rc != TB_OK) return rc;
     // the Gram feeds an inverse, which amplifies its error by the condition number: chunked accumulation
-    return launch_gemm(device, stream, px, g, px, g, dtype, k, k, G, ldg, nullptr, 1.0f, accumulate, 1, 1);
+    return launch_gemm(device, stream, px, g, px, g, dtype, k, k, G, ldg, nullptr, 1.0f, accumulate, 1,
+                       dtype == TB_F32 ? 1 : 0);
 }
 
 }  // extern "C"
