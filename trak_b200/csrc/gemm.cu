@@ -605,6 +605,51 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
     }
 }
 
+// The transposed fp32 case through shared memory: one CTA step = one [128 operand rows x 32 k]
+// tile, i.e. 32 source rows x 128 source columns.  Reads are 512-byte runs of source rows, and
+// after the transpose in shared memory each plane of the tile leaves as one contiguous 8 KB run
+// (the generic kernel's transposed stores are 16-byte pieces 64 bytes apart).
+__global__ void __launch_bounds__(256) pack_trans_f32_kernel(const float* __restrict__ src, uint16_t* __restrict__ packed,
+                                                             const uint32_t* __restrict__ amax, uint64_t rows, uint64_t K,
+                                                             uint64_t ld, uint32_t rowblocks, uint32_t kblocks) {
+    constexpr int LDS = 34;  // padded row of a plane tile, in 16-bit elements (17 words: conflict-free)
+    __shared__ __align__(16) uint16_t tile[2][128][LDS];
+    const uint32_t c = threadIdx.x & 127u, half = threadIdx.x >> 7;
+    const uint64_t ntiles = (uint64_t)rowblocks * kblocks;
+    for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const uint64_t rb = t % rowblocks, kb = t / rowblocks;  // neighbouring CTAs: neighbouring runs of the same source rows
+        const uint64_t R = rb * 128u + c;
+        const float up = R < rows ? row_scale_up(amax[R]) : 1.0f;
+#pragma unroll 4
+        for (uint32_t pass = 0; pass < 16; ++pass) {
+            const uint32_t kk = pass * 2u + half;
+            const uint64_t k = kb * 32u + kk;
+            float x = 0.0f;
+            if (R < rows && k < K) x = src[k * ld + R];
+            const float xs = x * up;
+            const __half h = __float2half_rn(xs);
+            const __half l = __float2half_rn(xs - __half2float(h));
+            tile[0][c][kk] = __half_as_ushort(h);
+            tile[1][c][kk] = __half_as_ushort(l);
+        }
+        __syncthreads();
+        uint16_t* dst = packed + (rb * kblocks + kb) * 2u * 128u * 32u;
+#pragma unroll
+        for (uint32_t it = 0; it < 4; ++it) {
+            const uint32_t q = it * 256u + threadIdx.x;       // 16-byte piece: plane, row, eighth
+            const uint32_t pl = q >> 9, r = (q >> 2) & 127u, oct = q & 3u;
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&tile[pl][r][oct * 8u]);
+            uint4 o;
+            o.x = w[0];
+            o.y = w[1];
+            o.z = w[2];
+            o.w = w[3];
+            *reinterpret_cast<uint4*>(dst + (size_t)q * 8u) = o;
+        }
+        __syncthreads();
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 Packed packed_geometry(int dtype, int64_t rows, int64_t K) {
     Packed g;
@@ -636,7 +681,9 @@ int launch_pack(const void* src, int dtype, bool trans, uint64_t rows, uint64_t 
             if (by > 65535) by = 65535;
             const uint64_t chunk = (K + by - 1) / by;
             amax_cols_kernel<<<dim3(bx, (uint32_t)((K + chunk - 1) / chunk)), 256, 0, stream>>>(s, amax, rows, K, ld, chunk);
-            pack_kernel<float, 2, true><<<nb, 256, 0, stream>>>(s, packed, amax, rows, K, ld, g.rowblocks, g.kblocks);
+            uint64_t tb = (uint64_t)g.rowblocks * g.kblocks;
+            if (tb > (uint64_t)sm_count * 16) tb = (uint64_t)sm_count * 16;
+            pack_trans_f32_kernel<<<(uint32_t)tb, 256, 0, stream>>>(s, packed, amax, rows, K, ld, g.rowblocks, g.kblocks);
         } else {
             uint64_t ab = (rows + 7) / 8;  // eight warps (rows) per CTA
             if (ab > cap) ab = cap;

@@ -3,12 +3,19 @@
 //
 // The reference calls torch.linalg.inv (LU).  A + lambda*I is symmetric positive definite, so this
 // goes through Cholesky, all in fp32:
-//   1. blocked right-looking Cholesky A = L L^T with 64-wide panels (diagonal block in one CTA,
-//      panel solve and trailing update as tiled fp32 kernels);
-//   2. W = L^-1, block column by block column from the last to the first;
-//   3. A^-1 = W^T W with the tensor-core GEMM of gemm.cu (symmetric mode, bf16 hi/lo split);
+//   1. blocked right-looking Cholesky A = L L^T with 64-wide panels: panel solve and trailing update
+//      as tiled fp32 kernels; the CTA that updates the first tile of the trailing block factors it
+//      right away (it is the next diagonal block) while the other CTAs finish the update, so the
+//      one-CTA factorisation is off the critical path;
+//   2. W = L^-1 bottom-up: the 64-wide diagonal blocks are inverted with the factorisation, then
+//      neighbouring blocks of size s = 64, 128, ... are merged, W21 = -W22 (L21 W11): all pairs of
+//      one size in two batched fp32 launches up to s = 512, tensor-core GEMMs (gemm.cu, chunked
+//      accumulation) from s = 1024 on;
+//   3. A^-1 = W^T W with the tensor-core GEMM of gemm.cu (symmetric mode, chunked accumulation);
 //   4. mean |entry| with a fixed-order two-pass reduction, then the rescale.
 // A non-positive pivot is recorded in the device status word (ST_NOT_SPD).
+#include <algorithm>
+
 #include "gemm.h"
 #include "host_util.h"
 #include "ptx.cuh"
@@ -16,7 +23,7 @@
 namespace tb {
 
 constexpr int NB = 64;      // panel width
-constexpr int TRTRI_SPLIT = 16;  // most parts the triangular-inverse product is split into
+constexpr int MERGE_TC_FROM = 1024;  // block size from which the merge products go to the tensor cores
 constexpr int TS = 68;      // padded row length of a shared-memory tile (floats)
 
 // acc[4][4] += sum_t At[t][ty*4 + i] * Bt[t][tx*4 + j]   (both tiles stored t-major)
@@ -55,37 +62,39 @@ __global__ void add_diag_kernel(float* A, int64_t lda, int k, float lambda) {
 }
 
 // Factor the jb x jb diagonal block (lower triangle) in shared memory, write L back, and write
-// inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.
-__global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, int jb, float* dinv,
-                                                        uint32_t* status) {
-    __shared__ float S[NB][NB + 1];
-    __shared__ float Winv[NB][NB + 1];
-    __shared__ int bad;
+// inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.  256 threads; S and Winv are two
+// shared 64 x 65 arrays.  Two barriers per column: the pivot's square root is taken by every
+// thread from the still unscaled diagonal entry and kept in `diag`, so nobody waits for one
+// thread to write it.
+__device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t* status, float (*S)[NB + 1],
+                           float (*Winv)[NB + 1], float* diag, int* bad) {
     const int tid = threadIdx.x;
-    if (tid == 0) bad = 0;
+    if (tid == 0) *bad = 0;
     for (int e = tid; e < NB * NB; e += 256) {
         const int i = e >> 6, j = e & 63;
         S[i][j] = (i < jb && j <= i) ? A[(int64_t)i * lda + j] : 0.0f;
         Winv[i][j] = 0.0f;
     }
     __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
     for (int c = 0; c < jb; ++c) {
+        const float d = S[c][c];
+        const float piv = sqrtf(d);
         if (tid == 0) {
-            const float d = S[c][c];
-            if (!(d > 0.0f)) bad = 1;
-            S[c][c] = sqrtf(d);
+            if (!(d > 0.0f)) *bad = 1;
+            diag[c] = piv;
         }
+        if (c + 1 + tid < jb) S[c + 1 + tid][c] /= piv;
         __syncthreads();
-        const float piv = S[c][c];
-        for (int i = c + 1 + tid; i < jb; i += 256) S[i][c] /= piv;
-        __syncthreads();
-        const int m = jb - c - 1;  // trailing size
-        for (int e = tid; e < m * m; e += 256) {
-            const int i = c + 1 + e / m, j = c + 1 + e % m;
-            if (j <= i) S[i][j] -= S[i][c] * S[j][c];
+        // trailing update of the lower triangle, 16 x 16 threads striding over it
+        for (int i = c + 1 + ty; i < jb; i += 16) {
+            const float li = S[i][c];
+            for (int j = c + 1 + tx; j <= i; j += 16) S[i][j] -= li * S[j][c];
         }
         __syncthreads();
     }
+    for (int c = tid; c < jb; c += 256) S[c][c] = diag[c];
+    __syncthreads();
     // inverse of the lower-triangular block by forward substitution: column c is handled by the four
     // lanes 4c..4c+3 of one warp, which split every dot product and combine with two shuffles
     {
@@ -109,7 +118,16 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, i
         if (i < jb && j <= i) A[(int64_t)i * lda + j] = S[i][j];
         dinv[e] = Winv[i][j];
     }
-    if (tid == 0 && bad) atomicCAS(status, 0u, (uint32_t)ST_NOT_SPD);
+    if (tid == 0 && *bad) atomicCAS(status, 0u, (uint32_t)ST_NOT_SPD);
+}
+
+__global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, int jb, float* dinv,
+                                                        uint32_t* status) {
+    __shared__ float S[NB][NB + 1];
+    __shared__ float Winv[NB][NB + 1];
+    __shared__ float diag[NB];
+    __shared__ int bad;
+    chol_block(A, lda, jb, dinv, status, S, Winv, diag, &bad);
 }
 
 // MODE 0 (Cholesky panel):  X[i, c] <- sum_t X[i, t] * D[c, t]      (X * D^T, in place)
@@ -144,11 +162,16 @@ __global__ void __launch_bounds__(256) panel_kernel(float* X, int64_t ldx, int r
 }
 
 // Trailing update of the Cholesky step:  C[i, j] -= sum_t P[i, t] * P[j, t]  for tiles on or below the
-// diagonal of the r x r trailing block; P is the r x jb panel (same leading dimension as C).
-__global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float* P, int64_t ld, int r, int jb) {
+// diagonal of the r x r trailing block; P is the r x jb panel (same leading dimension as C).  The CTA
+// of tile (0, 0) then holds the next diagonal block in its final state and factors it on the spot
+// (dinv_next = where its inverse goes), overlapping with the other CTAs' updates.
+__global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float* P, int64_t ld, int r, int jb,
+                                                          float* dinv_next, uint32_t* status) {
     if (blockIdx.x > blockIdx.y) return;  // tile column > tile row: upper part, not needed
     __shared__ __align__(16) float At[NB][TS];
     __shared__ __align__(16) float Bt[NB][TS];
+    __shared__ float diag[NB];
+    __shared__ int bad;
     const int i0 = blockIdx.y * NB, j0 = blockIdx.x * NB;
     const int rows = min(NB, r - i0), cols = min(NB, r - j0);
     load_tile_T(At, P + (int64_t)i0 * ld, ld, rows, jb);
@@ -164,61 +187,74 @@ __global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float*
             const int ii = ty * 4 + i, jj = tx * 4 + j;
             if (ii < rows && jj < cols) C[(int64_t)(i0 + ii) * ld + j0 + jj] -= acc[i][j];
         }
+    if (blockIdx.x == 0 && blockIdx.y == 0) {
+        __syncthreads();  // the tile is complete in global memory and the operand tiles are free
+        static_assert(sizeof(float[NB][TS]) >= sizeof(float[NB][NB + 1]), "tile storage is reused");
+        chol_block(C, ld, rows, dinv_next, status, reinterpret_cast<float(*)[NB + 1]>(&At[0][0]),
+                   reinterpret_cast<float(*)[NB + 1]>(&Bt[0][0]), diag, &bad);
+    }
 }
 
-// Inverse, step 2:  W21[i, c] <- - sum_{t <= i} W22[i, t] * T[t, c]
-// W22 is the already inverted lower-triangular trailing block (r x r), T is r x jb.  The sum over
-// t is split: CTA (bi, sp) adds the tiles bt = sp, sp + nsplit, ... <= bi of block row bi into
-// part[sp][i][c]; trtri_reduce_kernel then adds the parts in a fixed order and negates.
-__global__ void __launch_bounds__(256) trtri_partial_kernel(const float* W22, int64_t ld, const float* T,
-                                                            int64_t ldt, int r, int jb, float* part) {
+// Inverse of the triangular factor, bottom-up.  At block size s the matrix holds, in every aligned
+// diagonal block of size s, the finished inverse W of that block of L (upper triangle zero).  Pair p
+// joins the blocks at base = 2 s p:  W11 = [base, base + s),  W22 = the s2 = min(s, k - base - s)
+// rows after it, and the block below W11 still holds L21.  The inverse of the joined block needs
+//     W21 = - W22 (L21 W11),
+// computed as T = L21 W11 (STEP 0, into Tbuf[row][0..s)) and W21 = -W22 T (STEP 1, over L21).
+// One CTA per 64 x 64 tile of the result, blockIdx.z = pair; the triangles skip their zero tiles.
+template <int STEP>
+__global__ void __launch_bounds__(256) tri_merge_kernel(float* A, int64_t lda, int k, int s, float* Tbuf) {
     __shared__ __align__(16) float At[NB][TS];
     __shared__ __align__(16) float Bt[NB][TS];
-    const int bi = blockIdx.x, i0 = bi * NB, sp = blockIdx.y, nsplit = gridDim.y;
-    const int rows = min(NB, r - i0);
+    const int base = (int)blockIdx.z * 2 * s;
+    const int s2 = min(s, k - base - s);
+    const int i0 = blockIdx.y * NB, j0 = blockIdx.x * NB;
+    if (s2 <= 0 || i0 >= s2) return;
+    const int rows = min(NB, s2 - i0), cols = min(NB, s - j0);
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     float acc[4][4] = {};
-    for (int bt = sp; bt <= bi; bt += nsplit) {
-        const int t0 = bt * NB, tcols = min(NB, r - t0);
-        load_tile_T(At, W22 + (int64_t)i0 * ld + t0, ld, rows, tcols);
-        if (bt == bi) {  // diagonal tile of a lower-triangular matrix: drop what lies above the diagonal
-            __syncthreads();
-            for (int e = threadIdx.x; e < NB * NB; e += 256) {
-                const int i = e >> 6, t = e & 63;
-                if (t > i) At[t][i] = 0.0f;
-            }
+    const float* L21 = A + (int64_t)(base + s) * lda + base;
+    const float* W11 = A + (int64_t)base * lda + base;
+    const float* W22 = A + (int64_t)(base + s) * lda + base + s;
+    const float* T = Tbuf + (int64_t)(base + s) * s;
+    // STEP 0: t runs over the columns of L21 / rows of W11, and W11[t, j] = 0 for t < j
+    // STEP 1: t runs over the columns of W22 / rows of T,   and W22[i, t] = 0 for t > i
+    const int t_first = STEP == 0 ? j0 : 0;
+    const int t_end = STEP == 0 ? s : min(s2, i0 + NB);
+    for (int t0 = t_first; t0 < t_end; t0 += NB) {
+        const int tc = min(NB, t_end - t0);
+        if (STEP == 0) {
+            load_tile_T(At, L21 + (int64_t)i0 * lda + t0, lda, rows, tc);
+            load_tile_N(Bt, W11 + (int64_t)t0 * lda + j0, lda, tc, cols);
+        } else {
+            load_tile_T(At, W22 + (int64_t)i0 * lda + t0, lda, rows, tc);
+            load_tile_N(Bt, T + (int64_t)t0 * s + j0, s, tc, cols);
         }
-        load_tile_N(Bt, T + (int64_t)t0 * ldt, ldt, tcols, jb);
         __syncthreads();
         tile_mma(At, Bt, ty, tx, acc);
         __syncthreads();
     }
-    float* dst = part + ((size_t)sp * r + i0) * NB;
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int ii = ty * 4 + i, c = tx * 4 + j;
-            if (ii < rows) dst[(size_t)ii * NB + c] = acc[i][j];
+            const int ii = ty * 4 + i, jj = tx * 4 + j;
+            if (ii < rows && jj < cols) {
+                if (STEP == 0)
+                    Tbuf[(int64_t)(base + s + i0 + ii) * s + j0 + jj] = acc[i][j];
+                else
+                    A[(int64_t)(base + s + i0 + ii) * lda + base + j0 + jj] = -acc[i][j];
+            }
         }
 }
-__global__ void trtri_reduce_kernel(const float* part, int nsplit, int r, int jb, float* W21, int64_t ld) {
-    const int total = r * NB;
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
-        const int i = e >> 6, c = e & 63;
-        if (c >= jb) continue;
-        float s = 0.0f;
-        for (int sp = 0; sp < nsplit; ++sp) s += part[((size_t)sp * r + i) * NB + c];
-        W21[(int64_t)i * ld + c] = -s;
-    }
-}
 
-// A[j0.., j0..] diagonal block <- dinv block (lower), and zero the strict upper triangle of the
-// block row so that W is a clean lower-triangular matrix.
-__global__ void write_diag_inverse_kernel(float* A, int64_t lda, int k, int j0, int jb, const float* dinv) {
+// Every 64-wide diagonal block <- its inverse from the factorisation (lower, zero above); one CTA each.
+__global__ void write_diag_inverse_kernel(float* A, int64_t lda, int k, const float* dinv) {
+    const int j0 = blockIdx.x * NB, jb = min(NB, k - j0);
+    const float* D = dinv + (size_t)blockIdx.x * NB * NB;
     for (int e = threadIdx.x; e < NB * NB; e += blockDim.x) {
         const int i = e >> 6, j = e & 63;
-        if (i < jb && j < jb) A[(int64_t)(j0 + i) * lda + j0 + j] = dinv[e];
+        if (i < jb && j < jb) A[(int64_t)(j0 + i) * lda + j0 + j] = D[e];
     }
 }
 __global__ void zero_upper_kernel(float* A, int64_t lda, int k) {
@@ -266,24 +302,34 @@ __global__ void scale_by_inverse_kernel(float* A, int64_t lda, int k, const floa
 }
 
 struct InvLayout {
-    size_t dinv, tbuf, tpart, partial, mean, packed, total;
+    size_t dinv, partial, mean, scratch, total;
 };
+// Scratch of the merge at block size s (first block s rows, second block s2 rows): both packed
+// operands of the larger product and T; all of it is free again before W^T W is packed.
+static size_t merge_scratch_bytes(int64_t s, int64_t s2) {
+    const size_t pa = std::max(packed_geometry(TB_F32, s2, s).bytes, packed_geometry(TB_F32, s2, s2).bytes);
+    const size_t pb = packed_geometry(TB_F32, s, std::max(s, s2)).bytes;
+    return pa + pb + align_up((size_t)s2 * s * sizeof(float), 1024);
+}
 static InvLayout inv_layout(int64_t k) {
     InvLayout l;
     const size_t nblk = (size_t)((k + NB - 1) / NB);
     size_t off = 0;
     l.dinv = off;
     off += align_up(nblk * NB * NB * sizeof(float), 256);
-    l.tbuf = off;
-    off += align_up((size_t)k * NB * sizeof(float), 256);
-    l.tpart = off;
-    off += align_up((size_t)TRTRI_SPLIT * k * NB * sizeof(float), 256);
     l.partial = off;
     off += align_up(RED_BLOCKS * sizeof(double), 256);
     l.mean = off;
     off += 256;
-    l.packed = off;
-    off += packed_geometry(TB_F32, k, k).bytes;
+    l.scratch = off;
+    size_t need = packed_geometry(TB_F32, k, k).bytes;
+    for (int64_t s = NB; s < k; s *= 2) {
+        if (s < MERGE_TC_FROM)
+            need = std::max(need, align_up((size_t)k * s * sizeof(float), 1024));  // T of every pair
+        else
+            need = std::max(need, merge_scratch_bytes(s, std::min<int64_t>(s, k - s)));
+    }
+    off += need;
     l.total = off + 1024;
     return l;
 }
@@ -310,52 +356,76 @@ int tb_spd_inverse(int device, void* stream_, float* A, int64_t k, int64_t lda, 
     const InvLayout l = inv_layout(k);
     uint8_t* base = static_cast<uint8_t*>(ws);
     float* dinv = reinterpret_cast<float*>(base + l.dinv);
-    float* tbuf = reinterpret_cast<float*>(base + l.tbuf);
-    float* tpart = reinterpret_cast<float*>(base + l.tpart);
     double* partial = reinterpret_cast<double*>(base + l.partial);
     float* mean = reinterpret_cast<float*>(base + l.mean);
-    uint16_t* packed = reinterpret_cast<uint16_t*>(base + l.packed);
+    uint8_t* scratch = base + l.scratch;
     const int K = (int)k;
     const int nblk = (K + NB - 1) / NB;
 
     if (lambda != 0.0f) add_diag_kernel<<<(K + 255) / 256, 256, 0, stream>>>(A, lda, K, lambda);
 
-    // 1. Cholesky (lower triangle of A becomes L); dinv[b] = inverse of the b-th diagonal block of L
+    // 1. Cholesky (lower triangle of A becomes L); dinv[b] = inverse of the b-th diagonal block of L.
+    //    The first diagonal block is factored by its own launch, every later one inside the trailing
+    //    update that completes it.
+    chol_diag_kernel<<<1, 256, 0, stream>>>(A, lda, K < NB ? K : NB, dinv, status_ptr(device));
     for (int b = 0; b < nblk; ++b) {
         const int j0 = b * NB, jb = K - j0 < NB ? K - j0 : NB, r = K - j0 - jb;
-        float* Ajj = A + (int64_t)j0 * lda + j0;
-        chol_diag_kernel<<<1, 256, 0, stream>>>(Ajj, lda, jb, dinv + (size_t)b * NB * NB, status_ptr(device));
         if (r > 0) {
             float* A21 = A + (int64_t)(j0 + jb) * lda + j0;
             const int rt = (r + NB - 1) / NB;
             panel_kernel<0><<<rt, 256, 0, stream>>>(A21, lda, r, jb, dinv + (size_t)b * NB * NB, nullptr, 0);
-            syrk_update_kernel<<<dim3(rt, rt), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, A21, lda, r, jb);
+            syrk_update_kernel<<<dim3(rt, rt), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, A21, lda, r, jb,
+                                                                  dinv + (size_t)(b + 1) * NB * NB, status_ptr(device));
         }
     }
     TB_CUDA(cudaGetLastError());
 
-    // 2. W = L^-1, last block column first
-    for (int b = nblk - 1; b >= 0; --b) {
-        const int j0 = b * NB, jb = K - j0 < NB ? K - j0 : NB, r = K - j0 - jb;
-        const float* D = dinv + (size_t)b * NB * NB;
-        if (r > 0) {
-            float* L21 = A + (int64_t)(j0 + jb) * lda + j0;
-            const int rt = (r + NB - 1) / NB;
-            panel_kernel<1><<<rt, 256, 0, stream>>>(L21, lda, r, jb, D, tbuf, NB);
-            int nsplit = (2 * sm_count + rt - 1) / rt;  // about two CTAs per SM
-            if (nsplit > TRTRI_SPLIT) nsplit = TRTRI_SPLIT;
-            if (nsplit > rt) nsplit = rt;
-            trtri_partial_kernel<<<dim3(rt, nsplit), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, lda, tbuf,
-                                                                         NB, r, jb, tpart);
-            trtri_reduce_kernel<<<(r * NB + 255) / 256, 256, 0, stream>>>(tpart, nsplit, r, jb, L21, lda);
-        }
-        write_diag_inverse_kernel<<<1, 256, 0, stream>>>(A, lda, K, j0, jb, D);
-    }
+    // 2. W = L^-1: clear the upper triangle, put the inverted diagonal blocks in place, then merge
+    //    neighbouring blocks of size 64, 128, ...
     zero_upper_kernel<<<sm_count * 8, 256, 0, stream>>>(A, lda, K);
+    write_diag_inverse_kernel<<<nblk, 256, 0, stream>>>(A, lda, K, dinv);
+    for (int64_t s = NB; s < k; s *= 2) {
+        const int pairs = (int)((k + 2 * s - 1) / (2 * s));
+        if (s < MERGE_TC_FROM) {
+            float* Tbuf = reinterpret_cast<float*>(scratch);
+            const dim3 grid((unsigned)(s / NB), (unsigned)(s / NB), (unsigned)pairs);
+            tri_merge_kernel<0><<<grid, 256, 0, stream>>>(A, lda, K, (int)s, Tbuf);
+            tri_merge_kernel<1><<<grid, 256, 0, stream>>>(A, lda, K, (int)s, Tbuf);
+            continue;
+        }
+        for (int pr = 0; pr < pairs; ++pr) {
+            const int64_t b0 = (int64_t)pr * 2 * s, s2 = std::min<int64_t>(s, k - b0 - s);
+            if (s2 <= 0) continue;
+            float* W11 = A + b0 * lda + b0;
+            float* L21 = A + (b0 + s) * lda + b0;
+            float* W22 = A + (b0 + s) * lda + b0 + s;
+            const Packed g_l21 = packed_geometry(TB_F32, s2, s), g_w22 = packed_geometry(TB_F32, s2, s2);
+            const Packed g_w11t = packed_geometry(TB_F32, s, s), g_tt = packed_geometry(TB_F32, s, s2);
+            const size_t pa_bytes = std::max(g_l21.bytes, g_w22.bytes), pb_bytes = std::max(g_w11t.bytes, g_tt.bytes);
+            uint16_t* pa = reinterpret_cast<uint16_t*>(scratch);
+            uint16_t* pb = reinterpret_cast<uint16_t*>(scratch + pa_bytes);
+            float* T = reinterpret_cast<float*>(scratch + pa_bytes + pb_bytes);
+            // T[s2 x s] = L21 . W11 = L21 . (W11^T)^T
+            rc = launch_pack(L21, TB_F32, false, (uint64_t)s2, (uint64_t)s, (uint64_t)lda, pa, g_l21, sm_count, stream);
+            if (rc != TB_OK) return rc;
+            rc = launch_pack(W11, TB_F32, true, (uint64_t)s, (uint64_t)s, (uint64_t)lda, pb, g_w11t, sm_count, stream);
+            if (rc != TB_OK) return rc;
+            rc = launch_gemm(device, stream, pa, g_l21, pb, g_w11t, TB_F32, s2, s, T, s, nullptr, 1.0f, 0, 0, 1);
+            if (rc != TB_OK) return rc;
+            // W21[s2 x s] = - W22 . T = - W22 . (T^T)^T, written over L21
+            rc = launch_pack(W22, TB_F32, false, (uint64_t)s2, (uint64_t)s2, (uint64_t)lda, pa, g_w22, sm_count, stream);
+            if (rc != TB_OK) return rc;
+            rc = launch_pack(T, TB_F32, true, (uint64_t)s, (uint64_t)s2, (uint64_t)s, pb, g_tt, sm_count, stream);
+            if (rc != TB_OK) return rc;
+            rc = launch_gemm(device, stream, pa, g_w22, pb, g_tt, TB_F32, s2, s, L21, lda, nullptr, -1.0f, 0, 0, 1);
+            if (rc != TB_OK) return rc;
+        }
+    }
     TB_CUDA(cudaGetLastError());
 
     // 3. A^-1 = W^T W (full symmetric result written over A; the operand was packed first)
     {
+        uint16_t* packed = reinterpret_cast<uint16_t*>(scratch);
         const Packed g = packed_geometry(TB_F32, k, k);
         rc = launch_pack(A, TB_F32, true, (uint64_t)k, (uint64_t)k, (uint64_t)lda, packed, g, sm_count, stream);
         if (rc != TB_OK) return rc;
