@@ -3,10 +3,11 @@
 //
 // The reference calls torch.linalg.inv (LU).  A + lambda*I is symmetric positive definite, so this
 // goes through Cholesky, all in fp32:
-//   1. blocked right-looking Cholesky A = L L^T with 64-wide panels: panel solve and trailing update
-//      as tiled fp32 kernels; the CTA that updates the first tile of the trailing block factors it
-//      right away (it is the next diagonal block) while the other CTAs finish the update, so the
-//      one-CTA factorisation is off the critical path;
+//   1. two-level right-looking Cholesky A = L L^T: 64-wide steps (panel solve and update as tiled
+//      fp32 kernels) stay inside a 512-wide block column, and everything to the right of it gets
+//      one rank-512 update per block column from the tensor cores (gemm.cu, symmetric, chunked
+//      accumulation); the CTA that updates the first tile of the trailing block factors and inverts
+//      it right away (it is the next diagonal block) while the other CTAs finish the update;
 //   2. W = L^-1 bottom-up: the 64-wide diagonal blocks are inverted with the factorisation, then
 //      neighbouring blocks of size s = 64, 128, ... are merged, W21 = -W22 (L21 W11): all pairs of
 //      one size in two batched fp32 launches up to s = 512, tensor-core GEMMs (gemm.cu, chunked
@@ -23,6 +24,7 @@
 namespace tb {
 
 constexpr int NB = 64;      // panel width
+constexpr int OUTER = 512;    // block column of the two-level Cholesky
 constexpr int MERGE_TC_FROM = 1024;  // block size from which the merge products go to the tensor cores
 constexpr int TS = 68;      // padded row length of a shared-memory tile (floats)
 
@@ -61,73 +63,93 @@ __global__ void add_diag_kernel(float* A, int64_t lda, int k, float lambda) {
     if (i < k) A[(int64_t)i * lda + i] += lambda;
 }
 
-// Factor the jb x jb diagonal block (lower triangle) in shared memory, write L back, and write
-// inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.  256 threads; S and Winv are two
-// shared 64 x 65 arrays.  Two barriers per column: the pivot's square root is taken by every
-// thread from the still unscaled diagonal entry and kept in `diag`, so nobody waits for one
-// thread to write it.
-__device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t* status, float (*S)[NB + 1],
-                           float (*Winv)[NB + 1], float* diag, int* bad) {
-    const int tid = threadIdx.x;
+// Factors the jb x jb diagonal block A = L L^T and inverts L in the same sweep; writes L back over the
+// lower triangle and inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.  256 threads as a
+// 16 x 16 grid, each keeping a 4 x 4 piece of the block and of the inverse in registers.  Column c:
+// the owners publish the (still unscaled) column c of the block and row c of the inverse in shared
+// memory, one barrier, then every thread scales what it needs by 1/sqrt(pivot) and applies the
+// rank-one updates  S[i][j] -= L[i][c] L[j][c]  (i, j > c)  and  W[i][:] -= L[i][c] W[c][:]  (i > c:
+// forward elimination of [L | I]).  The buffers alternate between columns, so one barrier per column
+// is enough.  Rows and columns beyond jb are an identity block, which leaves the rest untouched.
+// `buf` is 256 floats of shared memory, `bad` one shared int.
+__device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t* status, float* buf, int* bad) {
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    float (*colbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf);
+    float (*rowbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf + 2 * NB);
+    float sblk[4][4], wblk[4][4];
     if (tid == 0) *bad = 0;
-    for (int e = tid; e < NB * NB; e += 256) {
-        const int i = e >> 6, j = e & 63;
-        S[i][j] = (i < jb && j <= i) ? A[(int64_t)i * lda + j] : 0.0f;
-        Winv[i][j] = 0.0f;
-    }
-    __syncthreads();
-    const int ty = tid >> 4, tx = tid & 15;
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty * 4 + a, j = tx * 4 + b;
+            sblk[a][b] = (i < jb && j <= i) ? A[(int64_t)i * lda + j] : (i == j ? 1.0f : 0.0f);
+            wblk[a][b] = i == j ? 1.0f : 0.0f;
+        }
     for (int c = 0; c < jb; ++c) {
-        const float d = S[c][c];
-        const float piv = sqrtf(d);
-        if (tid == 0) {
-            if (!(d > 0.0f)) *bad = 1;
-            diag[c] = piv;
-        }
-        if (c + 1 + tid < jb) S[c + 1 + tid][c] /= piv;
-        __syncthreads();
-        // trailing update of the lower triangle, 16 x 16 threads striding over it
-        for (int i = c + 1 + ty; i < jb; i += 16) {
-            const float li = S[i][c];
-            for (int j = c + 1 + tx; j <= i; j += 16) S[i][j] -= li * S[j][c];
-        }
-        __syncthreads();
-    }
-    for (int c = tid; c < jb; c += 256) S[c][c] = diag[c];
-    __syncthreads();
-    // inverse of the lower-triangular block by forward substitution: column c is handled by the four
-    // lanes 4c..4c+3 of one warp, which split every dot product and combine with two shuffles
-    {
-        const int c = tid >> 2, part = tid & 3;
-        if (part == 0 && c < jb) Winv[c][c] = 1.0f / S[c][c];
-        __syncwarp();
-        for (int i = 1; i < jb; ++i) {
-            float s = 0.0f;
-            if (c < i) {
-                for (int t = c + part; t < i; t += 4) s = fmaf(S[i][t], Winv[t][c], s);
+        const int pb = c & 1, cq = c >> 2, cr = c & 3;
+        if (tx == cq) {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                float v = sblk[a][0];
+                if (cr == 1) v = sblk[a][1];
+                if (cr == 2) v = sblk[a][2];
+                if (cr == 3) v = sblk[a][3];
+                colbuf[pb][ty * 4 + a] = v;
             }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (part == 0 && c < i) Winv[i][c] = -s / S[i][i];
-            __syncwarp();
+        }
+        if (ty == cq) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                float v = wblk[0][b];
+                if (cr == 1) v = wblk[1][b];
+                if (cr == 2) v = wblk[2][b];
+                if (cr == 3) v = wblk[3][b];
+                rowbuf[pb][tx * 4 + b] = v;
+            }
+        }
+        __syncthreads();
+        const float d = colbuf[pb][c];
+        if (tid == 0 && !(d > 0.0f)) *bad = 1;
+        const float rinv = 1.0f / sqrtf(d);
+        float li[4], lj[4], wr[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            li[a] = colbuf[pb][ty * 4 + a] * rinv;
+            lj[a] = colbuf[pb][tx * 4 + a] * rinv;
+            wr[a] = rowbuf[pb][tx * 4 + a] * rinv;
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int i = ty * 4 + a;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int j = tx * 4 + b;
+                if (i > c && j > c) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
+                if (j == c && i >= c) sblk[a][b] = li[a];          // column c of L, scaled
+                if (i > c) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
+                if (i == c) wblk[a][b] = wr[b];                    // row c of the inverse, scaled
+            }
         }
     }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty * 4 + a, j = tx * 4 + b;
+            const bool in = i < jb && j <= i;
+            if (in) A[(int64_t)i * lda + j] = sblk[a][b];
+            dinv[i * NB + j] = in ? wblk[a][b] : 0.0f;
+        }
     __syncthreads();
-    for (int e = tid; e < NB * NB; e += 256) {
-        const int i = e >> 6, j = e & 63;
-        if (i < jb && j <= i) A[(int64_t)i * lda + j] = S[i][j];
-        dinv[e] = Winv[i][j];
-    }
     if (tid == 0 && *bad) atomicCAS(status, 0u, (uint32_t)ST_NOT_SPD);
 }
 
 __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, int jb, float* dinv,
                                                         uint32_t* status) {
-    __shared__ float S[NB][NB + 1];
-    __shared__ float Winv[NB][NB + 1];
-    __shared__ float diag[NB];
+    __shared__ float buf[4 * NB];
     __shared__ int bad;
-    chol_block(A, lda, jb, dinv, status, S, Winv, diag, &bad);
+    chol_block(A, lda, jb, dinv, status, buf, &bad);
 }
 
 // MODE 0 (Cholesky panel):  X[i, c] <- sum_t X[i, t] * D[c, t]      (X * D^T, in place)
@@ -161,16 +183,16 @@ __global__ void __launch_bounds__(256) panel_kernel(float* X, int64_t ldx, int r
         }
 }
 
-// Trailing update of the Cholesky step:  C[i, j] -= sum_t P[i, t] * P[j, t]  for tiles on or below the
-// diagonal of the r x r trailing block; P is the r x jb panel (same leading dimension as C).  The CTA
-// of tile (0, 0) then holds the next diagonal block in its final state and factors it on the spot
-// (dinv_next = where its inverse goes), overlapping with the other CTAs' updates.
+// Trailing update of a Cholesky step:  C[i, j] -= sum_t P[i, t] * P[j, t]  for the tiles on or below
+// the diagonal in the first gridDim.x tile columns of the r x r trailing block; P is the r x jb panel
+// (same leading dimension as C).  The CTA of tile (0, 0) then holds the next diagonal block in its
+// final state and factors it on the spot (dinv_next = where its inverse goes), overlapping with the
+// other CTAs' updates.
 __global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float* P, int64_t ld, int r, int jb,
                                                           float* dinv_next, uint32_t* status) {
     if (blockIdx.x > blockIdx.y) return;  // tile column > tile row: upper part, not needed
     __shared__ __align__(16) float At[NB][TS];
     __shared__ __align__(16) float Bt[NB][TS];
-    __shared__ float diag[NB];
     __shared__ int bad;
     const int i0 = blockIdx.y * NB, j0 = blockIdx.x * NB;
     const int rows = min(NB, r - i0), cols = min(NB, r - j0);
@@ -187,11 +209,9 @@ __global__ void __launch_bounds__(256) syrk_update_kernel(float* C, const float*
             const int ii = ty * 4 + i, jj = tx * 4 + j;
             if (ii < rows && jj < cols) C[(int64_t)(i0 + ii) * ld + j0 + jj] -= acc[i][j];
         }
-    if (blockIdx.x == 0 && blockIdx.y == 0) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && dinv_next != nullptr) {
         __syncthreads();  // the tile is complete in global memory and the operand tiles are free
-        static_assert(sizeof(float[NB][TS]) >= sizeof(float[NB][NB + 1]), "tile storage is reused");
-        chol_block(C, ld, rows, dinv_next, status, reinterpret_cast<float(*)[NB + 1]>(&At[0][0]),
-                   reinterpret_cast<float(*)[NB + 1]>(&Bt[0][0]), diag, &bad);
+        chol_block(C, ld, rows, dinv_next, status, &At[0][0], &bad);
     }
 }
 
@@ -322,7 +342,7 @@ static InvLayout inv_layout(int64_t k) {
     l.mean = off;
     off += 256;
     l.scratch = off;
-    size_t need = packed_geometry(TB_F32, k, k).bytes;
+    size_t need = packed_geometry(TB_F32, k, k).bytes;  // also covers the r x OUTER panels of the Cholesky
     for (int64_t s = NB; s < k; s *= 2) {
         if (s < MERGE_TC_FROM)
             need = std::max(need, align_up((size_t)k * s * sizeof(float), 1024));  // T of every pair
@@ -365,17 +385,38 @@ int tb_spd_inverse(int device, void* stream_, float* A, int64_t k, int64_t lda, 
     if (lambda != 0.0f) add_diag_kernel<<<(K + 255) / 256, 256, 0, stream>>>(A, lda, K, lambda);
 
     // 1. Cholesky (lower triangle of A becomes L); dinv[b] = inverse of the b-th diagonal block of L.
-    //    The first diagonal block is factored by its own launch, every later one inside the trailing
-    //    update that completes it.
-    chol_diag_kernel<<<1, 256, 0, stream>>>(A, lda, K < NB ? K : NB, dinv, status_ptr(device));
-    for (int b = 0; b < nblk; ++b) {
-        const int j0 = b * NB, jb = K - j0 < NB ? K - j0 : NB, r = K - j0 - jb;
-        if (r > 0) {
+    //    Two levels: inside a block column of OUTER columns the 64-wide steps update only that block
+    //    column (fp32 tiles); what lies to its right gets one rank-OUTER update per block column from
+    //    the tensor cores (symmetric chunked GEMM, alpha = -1, accumulating).  The first diagonal block
+    //    of a block column is factored by its own launch, every other one inside the update that
+    //    completes it.
+    for (int o0 = 0; o0 < K; o0 += OUTER) {
+        const int o1 = o0 + OUTER < K ? o0 + OUTER : K;  // end of this block column
+        chol_diag_kernel<<<1, 256, 0, stream>>>(A + (int64_t)o0 * lda + o0, lda, o1 - o0 < NB ? o1 - o0 : NB,
+                                                dinv + (size_t)(o0 / NB) * NB * NB, status_ptr(device));
+        for (int j0 = o0; j0 < o1; j0 += NB) {
+            const int b = j0 / NB, jb = K - j0 < NB ? K - j0 : NB, r = K - j0 - jb;
+            if (r <= 0) break;
             float* A21 = A + (int64_t)(j0 + jb) * lda + j0;
             const int rt = (r + NB - 1) / NB;
             panel_kernel<0><<<rt, 256, 0, stream>>>(A21, lda, r, jb, dinv + (size_t)b * NB * NB, nullptr, 0);
-            syrk_update_kernel<<<dim3(rt, rt), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, A21, lda, r, jb,
-                                                                  dinv + (size_t)(b + 1) * NB * NB, status_ptr(device));
+            const int wt = (o1 - j0 - jb + NB - 1) / NB;  // tile columns left in the block column
+            if (wt > 0)
+                syrk_update_kernel<<<dim3(wt, rt), 256, 0, stream>>>(A + (int64_t)(j0 + jb) * lda + j0 + jb, A21, lda, r, jb,
+                                                                      dinv + (size_t)(b + 1) * NB * NB, status_ptr(device));
+        }
+        const int64_t r = K - o1;
+        if (r > 0) {
+            // A22 -= L21 L21^T with L21 = the r x (o1 - o0) block below this block column's diagonal block
+            const int64_t w = o1 - o0;
+            uint16_t* packed = reinterpret_cast<uint16_t*>(scratch);
+            const Packed g = packed_geometry(TB_F32, r, w);
+            rc = launch_pack(A + (int64_t)o1 * lda + o0, TB_F32, false, (uint64_t)r, (uint64_t)w, (uint64_t)lda, packed, g,
+                             sm_count, stream);
+            if (rc != TB_OK) return rc;
+            rc = launch_gemm(device, stream, packed, g, packed, g, TB_F32, r, r, A + (int64_t)o1 * lda + o1, lda, nullptr,
+                             -1.0f, 1, 1, 1);
+            if (rc != TB_OK) return rc;
         }
     }
     TB_CUDA(cudaGetLastError());
