@@ -472,27 +472,55 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const float fa = (p.amax_a && m < p.M) ? row_scale_down(p.amax_a[m]) : 1.0f;
 #pragma unroll
             for (int i = 0; i < 128; ++i) sum[i] = ((sum[i] * fa) * col_factor[chalf * 128u + i]) * rs;
-            if (m < p.M) {
-                float* dst = p.C + (int64_t)m * p.ldc + n0;
+            // C[m, n]: a lane holds one row, so storing from registers would touch 32 rows per
+            // instruction.  The pipeline buffers are idle by now (the last commit covered every MMA
+            // and every load has been consumed), so each warp turns its 32 x 128 block around in
+            // its own slab of them and stores rows of 128 consecutive floats.
+            {
+                constexpr uint32_t SLAB_LD = 129;  // odd row length: conflict-free both ways
+                float* slab = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                              (size_t)(warp - 4u) * 32u * SLAB_LD;
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    if (n0 + i < p.N && (!sym || n0 + i >= m)) {
-                        float v = sum[i];
-                        if (p.accumulate) v += dst[i];
-                        dst[i] = v;
-                    }
+                for (int i = 0; i < 128; ++i) slab[lane * SLAB_LD + i] = sum[i];
+                __syncwarp();
+                const uint32_t m_first = tile_m * 128u + q * 32u;
+                // four rows at a time: when accumulating, all sixteen loads are issued before the
+                // first store (a load behind a store to a possibly aliasing address would wait for it)
+#pragma unroll 1
+                for (uint32_t r0 = 0; r0 < 32u && m_first + r0 < p.M; r0 += 4u) {
+                    float v[4][4];
+                    bool on[4][4];
+#pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+                        for (uint32_t ch = 0; ch < 4; ++ch) {
+                            const uint32_t mr = m_first + r0 + u, n = n0 + ch * 32u + lane;
+                            on[u][ch] = mr < p.M && n < p.N && (!sym || n >= mr);
+                            v[u][ch] = (p.accumulate && on[u][ch]) ? p.C[(int64_t)mr * p.ldc + n] : 0.0f;
+                        }
+#pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+                        for (uint32_t ch = 0; ch < 4; ++ch)
+                            if (on[u][ch])
+                                p.C[(int64_t)(m_first + r0 + u) * p.ldc + n0 + ch * 32u + lane] =
+                                    v[u][ch] + slab[(r0 + u) * SLAB_LD + ch * 32u + lane];
                 }
             }
             if (sym && m < p.N) {
                 // C[n, m] gets the same bits: for a fixed i the warp's lanes hold consecutive m
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    if (n0 + i < p.M && n0 + i > m) {
-                        float* dst = p.C + (int64_t)(n0 + i) * p.ldc + m;
-                        float v = sum[i];
-                        if (p.accumulate) v += *dst;
-                        *dst = v;
+                for (int i0 = 0; i0 < 128; i0 += 16) {  // sixteen loads in flight, then sixteen stores
+                    float old[16];
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        const bool on = n0 + i0 + u < p.M && n0 + i0 + u > m;
+                        old[u] = (p.accumulate && on) ? p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] : 0.0f;
                     }
+#pragma unroll
+                    for (int u = 0; u < 16; ++u)
+                        if (n0 + i0 + u < p.M && n0 + i0 + u > m)
+                            p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] = sum[i0 + u] + old[u];
                 }
             }
         }

@@ -111,24 +111,40 @@ __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t*
         __syncthreads();
         const float d = colbuf[pb][c];
         if (tid == 0 && !(d > 0.0f)) *bad = 1;
-        const float rinv = 1.0f / sqrtf(d);
-        float li[4], lj[4], wr[4];
+        if (ty * 4 + 3 < c) continue;  // all of this thread's rows are above row c: nothing to do
+        // 1/sqrt(pivot): hardware estimate and one Newton step
+        float rinv = rsqrtf(d);
+        rinv = rinv * (1.5f - 0.5f * d * rinv * rinv);
+        float li[4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            li[a] = colbuf[pb][ty * 4 + a] * rinv;
-            lj[a] = colbuf[pb][tx * 4 + a] * rinv;
-            wr[a] = rowbuf[pb][tx * 4 + a] * rinv;
+        for (int a = 0; a < 4; ++a) li[a] = colbuf[pb][ty * 4 + a] * rinv;
+        if (tx * 4 + 3 >= c) {  // columns c and beyond: the block itself
+            float lj[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) lj[b] = colbuf[pb][tx * 4 + b] * rinv;
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int i = ty * 4 + a;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int j = tx * 4 + b;
+                    if (i > c && j > c) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
+                    if (j == c && i >= c) sblk[a][b] = li[a];  // column c of L, scaled
+                }
+            }
         }
+        if (tx * 4 <= c) {  // columns up to c: the inverse (row c of it is zero beyond column c)
+            float wr[4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            const int i = ty * 4 + a;
+            for (int b = 0; b < 4; ++b) wr[b] = rowbuf[pb][tx * 4 + b] * rinv;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int j = tx * 4 + b;
-                if (i > c && j > c) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
-                if (j == c && i >= c) sblk[a][b] = li[a];          // column c of L, scaled
-                if (i > c) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
-                if (i == c) wblk[a][b] = wr[b];                    // row c of the inverse, scaled
+            for (int a = 0; a < 4; ++a) {
+                const int i = ty * 4 + a;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (i > c) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
+                    if (i == c) wblk[a][b] = wr[b];  // row c of the inverse, scaled
+                }
             }
         }
     }
