@@ -93,6 +93,57 @@ __device__ __forceinline__ void gemm_fail(uint32_t* status, volatile uint32_t* a
     }
 }
 
+
+// Epilogue store of one warp's 32 x 128 block of results, which sits in the warp's shared-memory
+// slab as slab[row][column] (row length SLAB_LD floats: odd, so rows and columns are both
+// conflict-free).  C[m_first + row, n0 + column] is written as rows of 128 consecutive floats
+// (a lane holding one row in registers would touch 32 rows per store instruction).  When
+// accumulating, the loads of a group are all issued before its first store: a load behind a store
+// to a possibly aliasing address would wait for it.  Symmetric products store only n >= m that way
+// and write the same bits to C[n, m] for n > m (for a fixed column the lanes run along m: coalesced).
+constexpr uint32_t SLAB_LD = 129;
+constexpr uint32_t SLAB_FLOATS = 32u * SLAB_LD;
+__device__ __forceinline__ void store_block_from_slab(const GemmParams& p, const float* slab, uint32_t m_first,
+                                                      uint32_t n0, uint32_t lane) {
+    const bool sym = p.symmetric != 0;
+#pragma unroll 1
+    for (uint32_t r0 = 0; r0 < 32u && m_first + r0 < p.M; r0 += 4u) {
+        float v[4][4];
+        bool on[4][4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+            for (uint32_t ch = 0; ch < 4; ++ch) {
+                const uint32_t mr = m_first + r0 + u, n = n0 + ch * 32u + lane;
+                on[u][ch] = mr < p.M && n < p.N && (!sym || n >= mr);
+                v[u][ch] = (p.accumulate && on[u][ch]) ? p.C[(int64_t)mr * p.ldc + n] : 0.0f;
+            }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+            for (uint32_t ch = 0; ch < 4; ++ch)
+                if (on[u][ch])
+                    p.C[(int64_t)(m_first + r0 + u) * p.ldc + n0 + ch * 32u + lane] =
+                        v[u][ch] + slab[(r0 + u) * SLAB_LD + ch * 32u + lane];
+    }
+    const uint32_t m = m_first + lane;
+    if (sym && m < p.N) {
+#pragma unroll 1
+        for (uint32_t i0 = 0; i0 < 128u; i0 += 16u) {
+            float old[16];
+#pragma unroll
+            for (uint32_t u = 0; u < 16; ++u) {
+                const bool on = n0 + i0 + u < p.M && n0 + i0 + u > m;
+                old[u] = (p.accumulate && on) ? p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] : 0.0f;
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 16; ++u)
+                if (n0 + i0 + u < p.M && n0 + i0 + u > m)
+                    p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] = slab[lane * SLAB_LD + i0 + u] + old[u];
+        }
+    }
+}
+
 template <int NPL>
 __global__ void __launch_bounds__(384, 1)
 gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -224,49 +275,32 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else {
             tc_fence_after();
             const uint32_t lane_base = (q * 32u) << 16;
-            // symmetric product: every pair (m, n), n >= m, is taken from one accumulator entry and
-            // stored at C[m, n] and C[n, m], so the result is exactly symmetric
-            const bool sym = p.symmetric != 0;
+            // The pipeline buffers are idle by now (the commit behind bar_acc covered every MMA and
+            // every load has been consumed): each warp turns its 32 x 128 blocks around in its own slab.
+            float* slab = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                          (size_t)(warp - 4u) * SLAB_FLOATS;
 #pragma unroll 1
             for (uint32_t mb = 0; mb < 2; ++mb) {
-                const uint32_t m = tile_m * 256u + mb * 128u + q * 32u + lane;
+                const uint32_t m_first = tile_m * 256u + mb * 128u + q * 32u, m = m_first + lane;
                 const float rs = p.alpha * ((p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f);
                 const float fa = (p.amax_a && m < p.M) ? row_scale_down(p.amax_a[m]) : 1.0f;
 #pragma unroll 1
-                for (uint32_t cb = 0; cb < 8; ++cb) {
+                for (uint32_t cb = 0; cb < 8; cb += 2) {
                     const uint32_t c0 = chalf * 128u + cb * 16u;
-                    uint32_t r[16];
-                    tmem_ld_x16(tmem_base + lane_base + mb * 256u + c0, r);
+                    uint32_t r0[16], r1[16];
+                    tmem_ld_x16(tmem_base + lane_base + mb * 256u + c0, r0);
+                    tmem_ld_x16(tmem_base + lane_base + mb * 256u + c0 + 16u, r1);
                     tmem_wait_ld();
-                    const uint32_t n0 = tile_n * 256u + c0;
-                    float val[16];  // one value per entry: the mirrored store writes the same bits
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        val[j] = ((__uint_as_float(r[j]) * fa) * col_factor[c0 + j]) * rs;
-                    if (m < p.M) {
-                        float* dst = p.C + (int64_t)m * p.ldc + n0;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (n0 + j < p.N && (!sym || n0 + j >= m)) {
-                                float v = val[j];
-                                if (p.accumulate) v += dst[j];
-                                dst[j] = v;
-                            }
-                        }
-                    }
-                    if (sym && m < p.N) {
-                        // C[n, m]: for a fixed j the warp's lanes hold consecutive m -> coalesced
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (n0 + j < p.M && n0 + j > m) {
-                                float* dst = p.C + (int64_t)(n0 + j) * p.ldc + m;
-                                float v = val[j];
-                                if (p.accumulate) v += *dst;
-                                *dst = v;
-                            }
-                        }
+                    for (int j = 0; j < 16; ++j) {
+                        slab[lane * SLAB_LD + cb * 16u + j] = ((__uint_as_float(r0[j]) * fa) * col_factor[c0 + j]) * rs;
+                        slab[lane * SLAB_LD + cb * 16u + 16u + j] =
+                            ((__uint_as_float(r1[j]) * fa) * col_factor[c0 + 16u + j]) * rs;
                     }
                 }
+                __syncwarp();
+                store_block_from_slab(p, slab, m_first, tile_n * 256u + chalf * 128u, lane);
+                __syncwarp();  // the slab is rewritten for the second row block
             }
         }
     }
@@ -465,64 +499,20 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[set]));
         }
         if (ok) {
-            const bool sym = p.symmetric != 0;
             const uint32_t m = tile_m * 128u + q * 32u + lane;
             const uint32_t n0 = tile_n * 256u + chalf * 128u;
             const float rs = p.alpha * ((p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f);
             const float fa = (p.amax_a && m < p.M) ? row_scale_down(p.amax_a[m]) : 1.0f;
 #pragma unroll
             for (int i = 0; i < 128; ++i) sum[i] = ((sum[i] * fa) * col_factor[chalf * 128u + i]) * rs;
-            // C[m, n]: a lane holds one row, so storing from registers would touch 32 rows per
-            // instruction.  The pipeline buffers are idle by now (the last commit covered every MMA
-            // and every load has been consumed), so each warp turns its 32 x 128 block around in
-            // its own slab of them and stores rows of 128 consecutive floats.
-            {
-                constexpr uint32_t SLAB_LD = 129;  // odd row length: conflict-free both ways
-                float* slab = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
-                              (size_t)(warp - 4u) * 32u * SLAB_LD;
+            // The pipeline buffers are idle by now (the last commit covered every MMA and every load
+            // has been consumed), so each warp turns its 32 x 128 block around in its own slab of them.
+            float* slab = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw))) +
+                          (size_t)(warp - 4u) * SLAB_FLOATS;
 #pragma unroll
-                for (int i = 0; i < 128; ++i) slab[lane * SLAB_LD + i] = sum[i];
-                __syncwarp();
-                const uint32_t m_first = tile_m * 128u + q * 32u;
-                // four rows at a time: when accumulating, all sixteen loads are issued before the
-                // first store (a load behind a store to a possibly aliasing address would wait for it)
-#pragma unroll 1
-                for (uint32_t r0 = 0; r0 < 32u && m_first + r0 < p.M; r0 += 4u) {
-                    float v[4][4];
-                    bool on[4][4];
-#pragma unroll
-                    for (uint32_t u = 0; u < 4; ++u)
-#pragma unroll
-                        for (uint32_t ch = 0; ch < 4; ++ch) {
-                            const uint32_t mr = m_first + r0 + u, n = n0 + ch * 32u + lane;
-                            on[u][ch] = mr < p.M && n < p.N && (!sym || n >= mr);
-                            v[u][ch] = (p.accumulate && on[u][ch]) ? p.C[(int64_t)mr * p.ldc + n] : 0.0f;
-                        }
-#pragma unroll
-                    for (uint32_t u = 0; u < 4; ++u)
-#pragma unroll
-                        for (uint32_t ch = 0; ch < 4; ++ch)
-                            if (on[u][ch])
-                                p.C[(int64_t)(m_first + r0 + u) * p.ldc + n0 + ch * 32u + lane] =
-                                    v[u][ch] + slab[(r0 + u) * SLAB_LD + ch * 32u + lane];
-                }
-            }
-            if (sym && m < p.N) {
-                // C[n, m] gets the same bits: for a fixed i the warp's lanes hold consecutive m
-#pragma unroll
-                for (int i0 = 0; i0 < 128; i0 += 16) {  // sixteen loads in flight, then sixteen stores
-                    float old[16];
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) {
-                        const bool on = n0 + i0 + u < p.M && n0 + i0 + u > m;
-                        old[u] = (p.accumulate && on) ? p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] : 0.0f;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 16; ++u)
-                        if (n0 + i0 + u < p.M && n0 + i0 + u > m)
-                            p.C[(int64_t)(n0 + i0 + u) * p.ldc + m] = sum[i0 + u] + old[u];
-                }
-            }
+            for (int i = 0; i < 128; ++i) slab[lane * SLAB_LD + i] = sum[i];
+            __syncwarp();
+            store_block_from_slab(p, slab, tile_m * 128u + q * 32u, n0, lane);
         }
     }
 
