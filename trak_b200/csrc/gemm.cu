@@ -224,42 +224,46 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ph ^= 1u;
             }
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // -------------------------------- MMA issuer --------------------------------
+        // whole warp in the loop, one elected lane issues (descriptors stay in uniform registers)
+        const bool leader = elect_one();
         uint32_t slot = 0, ph = 0;
         bool ok = true;
         for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_full[slot]), ph, abort_flag)) {
-                gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, kb);
+            const bool got = mbar_wait(smem_u32(&bar_full[slot]), ph, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, kb);
                 ok = false;
                 break;
             }
             tc_fence_after();
             const uint32_t sa = smem_base + slot * STAGE_BYTES, sb = sa + A_BYTES;
+            const uint64_t b_hi = smem_desc_k_sw64(sb), b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES);
 #pragma unroll
             for (uint32_t mb = 0; mb < 2; ++mb) {
                 const uint32_t d = tmem_base + mb * 256u;
+                const uint64_t a_hi = smem_desc_k_sw64(sa + (mb * NPL) * GTILE_BYTES);
+                const uint64_t a_lo = smem_desc_k_sw64(sa + (mb * NPL + (NPL - 1)) * GTILE_BYTES);
+                if (leader) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < 2; ++kk) {
-                    const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-                    const uint64_t a_hi = smem_desc_k_sw64(sa + (mb * NPL) * GTILE_BYTES) + 2u * kk;
-                    const uint64_t b_hi = smem_desc_k_sw64(sb) + 2u * kk;
-                    umma_f16_ss(d, a_hi, b_hi, p.idesc, acc);
-                    if (NPL == 2) {
-                        const uint64_t a_lo = smem_desc_k_sw64(sa + (mb * NPL + 1) * GTILE_BYTES) + 2u * kk;
-                        const uint64_t b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES) + 2u * kk;
-                        umma_f16_ss(d, a_hi, b_lo, p.idesc, 1u);
-                        umma_f16_ss(d, a_lo, b_hi, p.idesc, 1u);
+                    for (uint32_t kk = 0; kk < 2; ++kk) {
+                        const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                        umma_f16_ss(d, a_hi + 2u * kk, b_hi + 2u * kk, p.idesc, acc);
+                        if (NPL == 2) {
+                            umma_f16_ss(d, a_hi + 2u * kk, b_lo + 2u * kk, p.idesc, 1u);
+                            umma_f16_ss(d, a_lo + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                        }
                     }
                 }
             }
-            tc_commit(smem_u32(&bar_empty[slot]));
+            if (leader) tc_commit(smem_u32(&bar_empty[slot]));
             if (++slot == S) {
                 slot = 0;
                 ph ^= 1u;
             }
         }
-        if (ok) tc_commit(smem_u32(&bar_acc));
+        if (ok && leader) tc_commit(smem_u32(&bar_acc));
     } else if (warp >= 4) {
         // --------------------------------- epilogue ---------------------------------
         const uint32_t q = warp & 3u, chalf = (warp - 4u) >> 2;  // TMEM lane quarter, column half
@@ -408,48 +412,56 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 ph ^= 1u;
             }
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // -------------------------------- MMA issuer --------------------------------
+        // The whole warp runs the loop and one elected lane issues: with warp-uniform control flow the
+        // descriptors and addresses stay in uniform registers, which the MMA and commit instructions
+        // take directly (computed under a one-lane branch each would be moved there first).
+        const bool leader = elect_one();
         uint32_t slot = 0, ph = 0;  // a chunk takes slots (slot, slot + 1); slot stays even, so no wrap inside one
-        for (uint32_t c = 0; c < nchunks; ++c) {
+        bool ok = true;
+        for (uint32_t c = 0; c < nchunks && ok; ++c) {
             const uint32_t set = c & 1u, use = c >> 1;
-            if (!mbar_wait(smem_u32(&bar_acc_empty[set]), (use & 1u) ^ 1u, abort_flag)) {
-                gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x10000u + c);
+            bool got = mbar_wait(smem_u32(&bar_acc_empty[set]), (use & 1u) ^ 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x10000u + c);
                 break;
             }
             tc_fence_after();
             const uint32_t d = tmem_base + set * 256u;
             const uint32_t nkb = min(2u, p.kblocks - 2u * c);
-            bool ok = true;
             // the small terms of the whole chunk first ...
-            for (uint32_t j = 0; j < nkb && ok; ++j) {
-                if (!mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag)) {
-                    gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, 2u * c + j);
+            for (uint32_t j = 0; j < nkb; ++j) {
+                got = mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) {
+                    if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, 2u * c + j);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+                const uint64_t a_hi = smem_desc_k_sw64(sa), a_lo = smem_desc_k_sw64(sa + GTILE_BYTES);
+                const uint64_t b_hi = smem_desc_k_sw64(sb), b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES);
+                if (leader) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < 2; ++kk) {
-                    const uint64_t a_hi = smem_desc_k_sw64(sa) + 2u * kk;
-                    const uint64_t a_lo = smem_desc_k_sw64(sa + GTILE_BYTES) + 2u * kk;
-                    const uint64_t b_hi = smem_desc_k_sw64(sb) + 2u * kk;
-                    const uint64_t b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES) + 2u * kk;
-                    umma_f16_ss(d, a_hi, b_lo, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
-                    umma_f16_ss(d, a_lo, b_hi, p.idesc, 1u);
+                    for (uint32_t kk = 0; kk < 2; ++kk) {
+                        umma_f16_ss(d, a_hi + 2u * kk, b_lo + 2u * kk, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
+                        umma_f16_ss(d, a_lo + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                    }
                 }
             }
             if (!ok) break;
             // ... then the large ones, releasing each slot as its last MMA is queued
             for (uint32_t j = 0; j < nkb; ++j) {
                 const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+                const uint64_t a_hi = smem_desc_k_sw64(sa), b_hi = smem_desc_k_sw64(sb);
+                if (leader) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < 2; ++kk)
-                    umma_f16_ss(d, smem_desc_k_sw64(sa) + 2u * kk, smem_desc_k_sw64(sb) + 2u * kk, p.idesc, 1u);
-                tc_commit(smem_u32(&bar_empty[slot + j]));
+                    for (uint32_t kk = 0; kk < 2; ++kk) umma_f16_ss(d, a_hi + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                    tc_commit(smem_u32(&bar_empty[slot + j]));
+                }
             }
-            tc_commit(smem_u32(&bar_acc_full[set]));
+            if (leader) tc_commit(smem_u32(&bar_acc_full[set]));
             slot += nkb;
             if (slot >= CK_SLOTS) {
                 slot = 0;
