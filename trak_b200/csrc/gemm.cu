@@ -430,7 +430,7 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tc_fence_after();
             const uint32_t d = tmem_base + set * 256u;
             const uint32_t nkb = min(2u, p.kblocks - 2u * c);
-            // the small terms of the whole chunk first ...
+            // per 32-k slot: its small terms first, then its large ones, and the slot is released
             for (uint32_t j = 0; j < nkb; ++j) {
                 got = mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag);
                 if (!__all_sync(0xffffffffu, got)) {
@@ -448,19 +448,12 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         umma_f16_ss(d, a_hi + 2u * kk, b_lo + 2u * kk, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
                         umma_f16_ss(d, a_lo + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
                     }
-                }
-            }
-            if (!ok) break;
-            // ... then the large ones, releasing each slot as its last MMA is queued
-            for (uint32_t j = 0; j < nkb; ++j) {
-                const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
-                const uint64_t a_hi = smem_desc_k_sw64(sa), b_hi = smem_desc_k_sw64(sb);
-                if (leader) {
 #pragma unroll
                     for (uint32_t kk = 0; kk < 2; ++kk) umma_f16_ss(d, a_hi + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
                     tc_commit(smem_u32(&bar_empty[slot + j]));
                 }
             }
+            if (!ok) break;
             if (leader) tc_commit(smem_u32(&bar_acc_full[set]));
             slot += nkb;
             if (slot >= CK_SLOTS) {
