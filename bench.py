@@ -268,7 +268,7 @@ def run_scoring(args, dev, rank, world, scale):
            "algorithmic_tflops": scoring_flop(n_total, k, m) / sec / 1e12,
            "roofline": {"bound": "tensor", "achieved": scoring_flop(n_total, k, m) / sec / 1e12 / world, "peak": peak,
                         "unit": "TFLOP/s", "frac": scoring_flop(n_total, k, m) / sec / 1e12 / world / peak,
-                        "note": "fp32 inputs run as bf16 hi/lo splits: three tensor-core passes per algorithmic flop, "
+                        "note": "fp32 inputs run as fp16 hi/lo splits: three tensor-core passes per algorithmic flop, "
                                 "so 1/3 of the bf16 peak is the ceiling of this figure"}}
     del X, scores, feats
     torch.cuda.empty_cache()

@@ -120,10 +120,14 @@ int tb_project_segments(int device, void *stream, const tb_segment *segs, int32_
 /* ---- after-kernel scoring -------------------------------------------------------
  * The three products and the inverse of the reference's BasicScoreComputer
  * (trak/score_computers.py:114-189).  Matrices are row-major; `dtype` is the type of
- * the inputs (TB_F16 / TB_BF16 / TB_F32), results are fp32.  fp32 inputs are split
- * into bf16 hi + lo planes and multiplied with three tensor-core passes (about 1e-5
- * relative error); 16-bit inputs are used as they are.  Workspaces: 256-byte aligned,
- * at least the size the matching *_workspace_bytes query returns.
+ * the inputs (TB_F16 / TB_BF16 / TB_F32), results are fp32.  fp32 inputs are scaled
+ * per operand row by a power of two, split into fp16 hi + lo planes and multiplied
+ * with three tensor-core passes: about 1e-5 relative error in tb_gemm_nt (one long
+ * tensor-core accumulation, which truncates), about 3e-7 in tb_gram and inside
+ * tb_spd_inverse (accumulated 64 k at a time and summed with rounded fp32 adds,
+ * because an inverse multiplies the Gram's error by its condition number); 16-bit
+ * inputs are used as they are.  Workspaces: 256-byte aligned, at least the size the
+ * matching *_workspace_bytes query returns.
  *
  * tb_gram        G[k x k] (+)= X^T X for X [n x k]            get_xtx, :145-155
  *                (full symmetric G; call it per row block with accumulate = 1)

@@ -5,7 +5,8 @@ arguments, same three methods, same shapes and dtypes of the results, so it can 
 passed to an unmodified ``TRAKer(score_computer=B200ScoreComputer)``
 (trak/traker.py:186-193).  Differences:
 
-* products run on the tensor cores (fp32 inputs as bf16 hi + lo planes, three passes);
+* products run on the tensor cores (fp32 inputs as row-scaled fp16 hi + lo planes, three
+  passes; the Gram is accumulated 64 rows at a time, so it is as accurate as an fp32 GEMM);
 * the regularised inverse goes through Cholesky in fp32 instead of LU and raises
   ``NotPositiveDefinite`` where the matrix is not positive definite;
 * Gram blocks are accumulated in fp32 whatever ``dtype`` is (the reference adds
