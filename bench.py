@@ -17,11 +17,13 @@ Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident 
 HBM; ``e2e`` is the same through the public ``trak_b200.fast_jl.project`` call with every
 step's batch copied from pinned host memory and its result read back (the copy of the next
 batch overlaps the current projection); ``roofline`` rates the
-projection kernel against the tensor-core peak; ``cpu_baseline`` is the CPU port of
-the reference's BasicProjector timed on a bounded sample on this box.
+projection kernel against the tensor-core peak; ``cpu_baseline`` is the reference's
+BasicProjector (or its CPU port, see below) timed on a bounded sample on this box.
 
-``--impl reference`` times that CPU port alone (all host threads) on the same
-workload, one bounded sample per step.  ``--scale f`` shrinks D by f (for profiler
+``--impl reference`` times the reference's CPU path alone (all host threads) on the same
+workload, one bounded sample per step: the unmodified ``BasicProjector`` from the reference
+package when its offline install is present under ``baseline/_ref`` (``kind`` "reference"),
+else the CPU port in ``oracle/`` (``kind`` "port").  ``--scale f`` shrinks D by f (for profiler
 captures of the same command on a small case).
 """
 import argparse
@@ -143,20 +145,56 @@ class ClockSampler:
 
 
 _cpu_input = {}
+_REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def reference_package():
+    """The reference's own Python package when its offline install travelled with the repository
+    (baseline/_ref, made by __graft_entry__.build() where the reference checkout exists), else None."""
+    if not os.path.isdir(os.path.join(_REF_DIR, "trak")):
+        return None
+    if _REF_DIR not in sys.path:
+        sys.path.insert(0, _REF_DIR)
+    try:
+        import trak
+        return trak
+    except Exception:
+        return None
+
+
+def cpu_kind():
+    return "reference" if reference_package() is not None else "port"
 
 
 def cpu_port_sample(rows, D, threads, blocks):
-    """Times the CPU port of BasicProjector on `blocks` of the ceil(k/100) column blocks."""
+    """Times the reference's CPU projection on `blocks` of the ceil(k/100) column blocks of 100: the
+    unmodified BasicProjector built with proj_dim = 100 * blocks (it then generates and multiplies exactly
+    the first `blocks` blocks of the full projection, same per-block seeds) when the reference package is
+    there, else its CPU port."""
     import torch
-    from oracle import basic_ref
     torch.set_num_threads(threads)
     if (rows, D) not in _cpu_input:  # the input is made once, outside the timed part
         _cpu_input.clear()
         _cpu_input[(rows, D)] = torch.randn(rows, D, generator=torch.Generator().manual_seed(1000)) * 1e-2
     g = _cpu_input[(rows, D)]
-    t0 = time.perf_counter()
-    basic_ref.basic_project(g, K_DIM, SEED, "normal", blocks=range(blocks))
-    dt = time.perf_counter() - t0
+    trak = reference_package()
+    if trak is not None:
+        proj = trak.projectors.BasicProjector(grad_dim=D, proj_dim=BLOCK * blocks, seed=SEED, proj_type="normal",
+                                              device="cpu", block_size=BLOCK, dtype=torch.float32)
+        if blocks == 1:  # a one-block projector keeps its matrix from the constructor; generate it in the timed part
+            t0 = time.perf_counter()
+            proj.generate_sketch_matrix(proj.generator_states[0])
+            proj.project(g, model_id=0)
+        else:
+            t0 = time.perf_counter()
+            proj.project(g, model_id=0)
+        dt = time.perf_counter() - t0
+        proj.free_memory()
+    else:
+        from oracle import basic_ref
+        t0 = time.perf_counter()
+        basic_ref.basic_project(g, K_DIM, SEED, "normal", blocks=range(blocks))
+        dt = time.perf_counter() - t0
     nblocks = -(-K_DIM // BLOCK)
     return dt * nblocks / blocks, dt  # extrapolated full-step seconds, measured seconds
 
@@ -167,7 +205,7 @@ def run_reference(args, D):
         return
     import torch
     threads = os.cpu_count() or 1
-    blocks = 1
+    blocks = 2
     nblocks = -(-K_DIM // BLOCK)
     for _ in range(args.warmup):
         cpu_port_sample(ROWS, D, threads, blocks)
@@ -177,7 +215,8 @@ def run_reference(args, D):
         full.append(s)
     sec = sum(full) / len(full)
     value = ROWS / sec
-    sample = (f"each step: all {ROWS} rows x D={D} projected onto {blocks} of {nblocks} column blocks of "
+    who = "the reference's unmodified BasicProjector" if cpu_kind() == "reference" else "CPU port of BasicProjector"
+    sample = (f"{who}: each step projects all {ROWS} rows x D={D} onto {blocks} of {nblocks} column blocks of "
               f"{BLOCK} (matrix block generated + matmul), time scaled by {nblocks}/{blocks}")
     line = {
         "impl": "reference", "metric": "jl_projected_examples_per_s", "value": value, "unit": "examples/s",
@@ -185,7 +224,7 @@ def run_reference(args, D):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(D),
         "cpu_baseline": {"value": value, "unit": "examples/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+                         "kind": cpu_kind(), "sample": sample},
         "e2e": {"value": value, "unit": "examples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -283,22 +322,32 @@ def scoring_cpu_baseline(threads):
     n, k, m = 8192, SC_K, 512
     X = torch.randn(n, k, generator=torch.Generator().manual_seed(1)) / k ** 0.5
     T = torch.randn(m, k, generator=torch.Generator().manual_seed(2)) / k ** 0.5
+    trak = reference_package()
+    if trak is not None:  # the reference's own class on the host cores
+        ref = trak.score_computers.BasicScoreComputer(dtype=torch.float32, device="cpu", logging_level=40,
+                                                      lambda_reg=SC_LAMBDA)
+        xtx, x_xtx_inv, scores = ref.get_xtx, ref.get_x_xtx_inv, ref.get_scores
+    else:
+        xtx = basic_ref.xtx
+        x_xtx_inv = lambda x, g: basic_ref.x_xtx_inv(x, g, SC_LAMBDA)  # noqa: E731
+        scores = basic_ref.scores
     t0 = time.perf_counter()
-    g = basic_ref.xtx(X)
+    g = xtx(X)
     t1 = time.perf_counter()
-    f = basic_ref.x_xtx_inv(X, g + (SC_N / n - 1) * torch.eye(k), SC_LAMBDA)  # keep the sample well conditioned
+    f = x_xtx_inv(X, g + (SC_N / n - 1) * torch.eye(k))  # keep the sample well conditioned
     t2 = time.perf_counter()
     acc = torch.zeros(n, m)
-    basic_ref.scores(f, T, acc)
+    scores(f, T, acc)
     t3 = time.perf_counter()
     # Gram and features grow with n, scores with n*m; the inverse (part of t2 - t1) is size-independent:
     # timed separately below
     t4 = time.perf_counter()
-    basic_ref.xtx_inverse(g + (SC_N / n) * torch.eye(k), SC_LAMBDA)
+    torch.linalg.inv(g + (SC_N / n) * torch.eye(k) + SC_LAMBDA * torch.eye(k))
     t_inv = time.perf_counter() - t4
     full = (t1 - t0) * SC_N / n + t_inv + max(0.0, (t2 - t1) - t_inv) * SC_N / n + (t3 - t2) * (SC_N / n) * (SC_M / m)
-    return {"value": full, "unit": "s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"CPU port of BasicScoreComputer at k={k} on {n} rows x {m} targets "
+    who = "the reference's unmodified BasicScoreComputer" if trak is not None else "CPU port of BasicScoreComputer"
+    return {"value": full, "unit": "s", "cores": torch.get_num_threads(), "kind": cpu_kind(),
+            "sample": f"{who} at k={k} on {n} rows x {m} targets "
                       f"(gram {t1 - t0:.1f} s, inverse {t_inv:.1f} s, features {t2 - t1 - t_inv:.1f} s, scores {t3 - t2:.1f} s), "
                       f"Gram/features scaled by n, scores by n*m, inverse counted once"}
 
@@ -449,9 +498,10 @@ def run_ours(args, D):
             threads = os.cpu_count() or 1
             sec, measured = cpu_port_sample(ROWS, D, threads, 2)
             nblocks = -(-K_DIM // BLOCK)
+            who = "the reference's unmodified BasicProjector" if cpu_kind() == "reference" else "CPU port of BasicProjector"
             line["cpu_baseline"] = {
-                "value": ROWS / sec, "unit": "examples/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"CPU port of BasicProjector (normal, fp32): all {ROWS} rows x D={D} onto 2 of "
+                "value": ROWS / sec, "unit": "examples/s", "cores": torch.get_num_threads(), "kind": cpu_kind(),
+                "sample": f"{who} (normal, fp32): all {ROWS} rows x D={D} onto 2 of "
                           f"{nblocks} column blocks of {BLOCK} in {measured:.1f} s, scaled by {nblocks}/2"}
         print(json.dumps(line), flush=True)
     if world > 1:
