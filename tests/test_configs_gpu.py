@@ -115,3 +115,43 @@ def test_gpt2_small_sized_gradients_through_the_chunked_projector(cuda):
     ratio = np.linalg.norm(got[4:], axis=1) / (gn * N ** 0.5)
     assert np.abs(ratio - 1).max() < 0.05, ratio
     assert starts[-1] == 124_439_808
+
+
+def test_cifar_resnet18_per_sample_gradients_to_2048_rademacher(cuda):
+    """CIFAR ResNet-18 (3x3 stem, 10 classes: 11,173,962 parameters in 62 tensors), per-example margin gradients
+    from torch.func in fp32, projected straight from the gradient dict: bit-equal to projecting the flattened
+    [B, D] matrix, and within tolerance of the fp64 host product with the fast_jl matrix."""
+    torchvision = pytest.importorskip("torchvision")
+    from torch.func import functional_call, grad, vmap
+    from trak_b200 import fast_jl
+    from trak_b200.projectors import CudaProjector, ProjectionType, vectorize
+    torch.manual_seed(0)
+    model = torchvision.models.resnet18(num_classes=10)
+    model.conv1 = torch.nn.Conv2d(3, 64, 3, 1, 1, bias=False)
+    model.maxpool = torch.nn.Identity()
+    model = model.to(cuda).eval()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    D = sum(p.numel() for p in params.values())
+    assert D == 11_173_962 and len(params) == 62
+    g = torch.Generator().manual_seed(0)
+    B, N, seed = 16, 2048, 0
+    xs, ys = torch.rand(B, 3, 32, 32, generator=g).to(cuda), torch.randint(0, 10, (B,), generator=g).to(cuda)
+
+    def margin(p, x, y):   # the image-classification model output of trak/modelout_functions.py:100-152
+        logits = functional_call(model, (p, buffers), (x.unsqueeze(0),))[0]
+        own = torch.arange(logits.numel(), device=logits.device) == y
+        rest = torch.logsumexp(torch.where(own, torch.full_like(logits, -torch.inf), logits), 0)
+        return (logits * own).sum() - rest
+
+    grads = vmap(grad(margin), in_dims=(None, 0, 0))(params, xs, ys)
+    proj = CudaProjector(D, N, seed, ProjectionType.rademacher, cuda, 32)
+    feats = proj.project(grads, model_id=0)
+    flat = vectorize(grads, device=cuda)
+    assert flat.shape == (B, D) and flat.dtype == torch.float32
+    assert torch.equal(feats, fast_jl.project_rademacher_16(flat, N, seed, proj.num_sms))
+    rows = [0, B - 1]
+    ref = o.project(o.RADEMACHER, flat[rows].cpu().numpy(), N, seed, proj.num_sms, round_f16=True)
+    got = feats[rows].cpu().numpy().astype(np.float64)
+    rel = np.linalg.norm(got - ref, axis=1) / np.linalg.norm(ref, axis=1)
+    assert rel.max() <= 1e-3, rel
