@@ -9,8 +9,9 @@ Multi-GPU: one process per GPU (torchrun), every rank projects its own batch of
 128 examples with the same virtual matrix -- the path shards by example, there is
 no data-path collective (weak scaling).
 
-After the projection, the second hot path is measured too (key ``scoring`` of the same
-line): the whole C4 scoring job -- X fp32 [1,000,000 x 8192] sharded by rows over the GPUs,
+After the projection, one featurize step of the CIFAR ResNet-18 configuration (key ``featurize``:
+torch.func gradients -> projection from the gradient dict) and the second hot path are measured
+too (key ``scoring`` of the same line): the whole C4 scoring job -- X fp32 [1,000,000 x 8192] sharded by rows over the GPUs,
 Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000 targets.
 
 Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
@@ -352,6 +353,85 @@ def scoring_cpu_baseline(threads):
                       f"Gram/features scaled by n, scores by n*m, inverse counted once"}
 
 
+# ---- end-to-end featurize step (per-sample gradients -> projection) ------------------------------
+def run_featurize(dev, rank, world):
+    """One featurize step as TRAKer runs it (trak/traker.py:424-429) on the CIFAR ResNet-18 configuration:
+    a batch of 128 synthetic 3x32x32 images copied from pinned host memory, per-example margin gradients from
+    torch.func (vmap(grad), fp32, 62 tensors, 11,173,962 features), Rademacher projection to k = 2048 straight
+    from the gradient dict with 1/sqrt(D) folded in, features copied back to the host.  Reports examples/s over
+    all ranks and how the step splits between PyTorch's gradients and the projection."""
+    import torch
+    import torch.distributed as dist
+    try:
+        import torchvision
+    except Exception as e:  # no torchvision: nothing to measure
+        return {"unavailable": f"torchvision not importable: {e}"}
+    from torch.func import functional_call, grad, vmap
+    from trak_b200 import fast_jl
+    from trak_b200.projectors import CudaProjector, ProjectionType
+
+    torch.manual_seed(0)
+    model = torchvision.models.resnet18(num_classes=10)
+    model.conv1 = torch.nn.Conv2d(3, 64, 3, 1, 1, bias=False)
+    model.maxpool = torch.nn.Identity()
+    model = model.to(dev).eval()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    D = sum(p.numel() for p in params.values())
+    B, N = 128, 2048
+    gen = torch.Generator().manual_seed(rank)
+    host_x = torch.rand(B, 3, 32, 32, generator=gen).pin_memory()
+    host_y = torch.randint(0, 10, (B,), generator=gen).pin_memory()
+    host_out = torch.empty(B, N).pin_memory()
+
+    def margin(p, x, y):
+        logits = functional_call(model, (p, buffers), (x.unsqueeze(0),))[0]
+        own = torch.arange(logits.numel(), device=logits.device) == y
+        rest = torch.logsumexp(torch.where(own, torch.full_like(logits, -torch.inf), logits), 0)
+        return (logits * own).sum() - rest
+
+    per_sample = vmap(grad(margin), in_dims=(None, 0, 0))
+    proj = CudaProjector(D, N, 0, ProjectionType.rademacher, dev, 32)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+
+    def step(timed):
+        x = host_x.to(dev, non_blocking=True)
+        y = host_y.to(dev, non_blocking=True)
+        if timed:
+            ev[0].record()
+        grads = per_sample(params, x, y)
+        if timed:
+            ev[1].record()
+        feats = proj.project(grads, model_id=0, alpha=1.0 / D ** 0.5)
+        if timed:
+            ev[2].record()
+        host_out.copy_(feats, non_blocking=True)
+        del grads
+
+    for _ in range(2):
+        step(False)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps, g_ms, p_ms = 5, 0.0, 0.0
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step(True)
+        torch.cuda.synchronize()
+        g_ms += ev[0].elapsed_time(ev[1])
+        p_ms += ev[1].elapsed_time(ev[2])
+    sec = torch.tensor([(time.perf_counter() - t0) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+    fast_jl.free_workspaces()
+    del model, params, proj
+    torch.cuda.empty_cache()
+    return {"metric": "featurize_examples_per_s", "value": world * B / sec.item(), "unit": "examples/s",
+            "config": {"workload": f"CIFAR ResNet-18 ({D} parameters, 62 tensors, fp32), batch {B} per GPU, "
+                                   f"vmap(grad) margins -> Rademacher k={N}, host images in, host features out"},
+            "ms_per_step": sec.item() * 1e3, "gradients_ms": g_ms / steps, "projection_ms": p_ms / steps}
+
+
 def run_ours(args, D):
     import torch
     import torch.distributed as dist
@@ -468,6 +548,10 @@ def run_ours(args, D):
     fast_jl.free_workspaces()
     torch.cuda.empty_cache()
     scoring = None if args.no_scoring else run_scoring(args, dev, rank, world, args.scale)
+    try:
+        featurize = None if args.no_scoring else run_featurize(dev, rank, world)
+    except Exception as e:  # an extra measurement must not take the main line down
+        featurize = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
 
     if rank == 0:
         peak, peak_note = measured_peaks()
@@ -490,6 +574,8 @@ def run_ours(args, D):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
         }
+        if featurize is not None:
+            line["featurize"] = featurize
         if scoring is not None:
             line["scoring"] = scoring
             if world == 1 and not args.no_cpu_baseline:
@@ -518,7 +604,8 @@ def main():
     ap.add_argument("--proj-type", choices=["normal", "rademacher"], default="normal",
                     help="normal = the benchmark workload; rademacher for profiling the other matrix type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-scoring", action="store_true", help="skip the after-kernel scoring measurement")
+    ap.add_argument("--no-scoring", action="store_true",
+                    help="skip the after-kernel scoring and the featurize-step measurements")
     args = ap.parse_args()
     D = max(1024, int(D_FULL * args.scale))
     if args.impl == "reference":
