@@ -66,18 +66,23 @@ __global__ void add_diag_kernel(float* A, int64_t lda, int k, float lambda) {
 // Factors the jb x jb diagonal block A = L L^T and inverts L in the same sweep; writes L back over the
 // lower triangle and inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.  256 threads as a
 // 16 x 16 grid, each keeping a 4 x 4 piece of the block and of the inverse in registers.  Column c:
-// the owners publish the (still unscaled) column c of the block and row c of the inverse in shared
-// memory, one barrier, then every thread scales what it needs by 1/sqrt(pivot) and applies the
-// rank-one updates  S[i][j] -= L[i][c] L[j][c]  (i, j > c)  and  W[i][:] -= L[i][c] W[c][:]  (i > c:
-// forward elimination of [L | I]).  The buffers alternate between columns, so one barrier per column
-// is enough.  Rows and columns beyond jb are an identity block, which leaves the rest untouched.
-// `buf` is 256 floats of shared memory, `bad` one shared int.
+// the owners publish the current column c of the block and row c of the inverse in shared memory,
+// one barrier, then every thread applies the rank-one updates
+//     S[i][j] -= S[i][c] S[j][c] / pivot   (i, j > c),     W[i][:] -= S[i][c] W[c][:] / pivot   (i > c)
+// (the second is forward elimination of [L | I]) with r = 1/sqrt(pivot) folded into both factors and
+// the operands of rows and columns <= c replaced by zero, so the sixteen multiply-adds of a piece need
+// no predicates.  Column c of the block and row c of the inverse are final after step c up to the
+// factor r, which is kept per column and applied once at the end.  The buffers alternate between
+// columns, so one barrier per column is enough.  Rows and columns beyond jb are an identity block.
+// `buf` is 5 * 64 floats of shared memory, `bad` one shared int.
 __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t* status, float* buf, int* bad) {
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     float (*colbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf);
     float (*rowbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf + 2 * NB);
+    float* rscale = buf + 4 * NB;
     float sblk[4][4], wblk[4][4];
     if (tid == 0) *bad = 0;
+    if (tid < NB) rscale[tid] = 1.0f;
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -110,52 +115,45 @@ __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t*
         }
         __syncthreads();
         const float d = colbuf[pb][c];
-        if (tid == 0 && !(d > 0.0f)) *bad = 1;
-        if (ty * 4 + 3 < c) continue;  // all of this thread's rows are above row c: nothing to do
         // 1/sqrt(pivot): hardware estimate and one Newton step
-        float rinv = rsqrtf(d);
-        rinv = rinv * (1.5f - 0.5f * d * rinv * rinv);
+        float r = rsqrtf(d);
+        r = r * (1.5f - 0.5f * d * r * r);
+        if (tid == 0) {
+            if (!(d > 0.0f)) *bad = 1;
+            rscale[c] = r;
+        }
+        if (ty * 4 + 3 <= c) continue;  // none of this thread's rows lies below row c
         float li[4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) li[a] = colbuf[pb][ty * 4 + a] * rinv;
-        if (tx * 4 + 3 >= c) {  // columns c and beyond: the block itself
+        for (int a = 0; a < 4; ++a) li[a] = ty * 4 + a > c ? colbuf[pb][ty * 4 + a] * r : 0.0f;
+        if (tx * 4 + 3 > c) {  // columns beyond c: the block itself
             float lj[4];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) lj[b] = colbuf[pb][tx * 4 + b] * rinv;
+            for (int b = 0; b < 4; ++b) lj[b] = tx * 4 + b > c ? colbuf[pb][tx * 4 + b] * r : 0.0f;
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const int i = ty * 4 + a;
+            for (int a = 0; a < 4; ++a)
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const int j = tx * 4 + b;
-                    if (i > c && j > c) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
-                    if (j == c && i >= c) sblk[a][b] = li[a];  // column c of L, scaled
-                }
-            }
+                for (int b = 0; b < 4; ++b) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
         }
-        if (tx * 4 <= c) {  // columns up to c: the inverse (row c of it is zero beyond column c)
+        if (tx * 4 <= c) {  // columns up to c: the inverse (its row c is zero beyond column c)
             float wr[4];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) wr[b] = rowbuf[pb][tx * 4 + b] * rinv;
+            for (int b = 0; b < 4; ++b) wr[b] = rowbuf[pb][tx * 4 + b] * r;
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const int i = ty * 4 + a;
+            for (int a = 0; a < 4; ++a)
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    if (i > c) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
-                    if (i == c) wblk[a][b] = wr[b];  // row c of the inverse, scaled
-                }
-            }
+                for (int b = 0; b < 4; ++b) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
         }
     }
+    __syncthreads();
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const int i = ty * 4 + a, j = tx * 4 + b;
             const bool in = i < jb && j <= i;
-            if (in) A[(int64_t)i * lda + j] = sblk[a][b];
-            dinv[i * NB + j] = in ? wblk[a][b] : 0.0f;
+            if (in) A[(int64_t)i * lda + j] = sblk[a][b] * rscale[j];
+            dinv[i * NB + j] = in ? wblk[a][b] * rscale[i] : 0.0f;
         }
     __syncthreads();
     if (tid == 0 && *bad) atomicCAS(status, 0u, (uint32_t)ST_NOT_SPD);
@@ -163,7 +161,7 @@ __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t*
 
 __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, int jb, float* dinv,
                                                         uint32_t* status) {
-    __shared__ float buf[4 * NB];
+    __shared__ float buf[5 * NB];
     __shared__ int bad;
     chol_block(A, lda, jb, dinv, status, buf, &bad);
 }
