@@ -549,7 +549,7 @@ def run_ours(args, D):
     torch.cuda.empty_cache()
     scoring = None if args.no_scoring else run_scoring(args, dev, rank, world, args.scale)
     try:
-        featurize = None if args.no_scoring else run_featurize(dev, rank, world)
+        featurize = None if (args.no_scoring or args.no_featurize) else run_featurize(dev, rank, world)
     except Exception as e:  # an extra measurement must not take the main line down
         featurize = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
 
@@ -604,6 +604,8 @@ def main():
     ap.add_argument("--proj-type", choices=["normal", "rademacher"], default="normal",
                     help="normal = the benchmark workload; rademacher for profiling the other matrix type")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-featurize", action="store_true",
+                    help="skip the featurize-step measurement (thousands of small PyTorch launches: slow under a profiler)")
     ap.add_argument("--no-scoring", action="store_true",
                     help="skip the after-kernel scoring and the featurize-step measurements")
     args = ap.parse_args()
