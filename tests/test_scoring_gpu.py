@@ -187,3 +187,38 @@ def test_ill_conditioned_gram_keeps_the_scores_accurate(cuda):
     inv /= inv.abs().mean()
     err = rel(acc, Xd @ inv @ Td.T)
     assert err <= 2e-4, err
+
+
+@pytest.mark.parametrize("k", [511, 513, 1000, 1025, 1537, 2049, 3000])
+def test_inverse_at_sizes_around_the_block_boundaries(cuda, k):
+    """Sizes on both sides of the 512-wide block columns of the Cholesky and of the 1024 threshold from which the
+    triangular merges run on the tensor cores, with ragged last blocks: inverse against an fp64 solve."""
+    from trak_b200 import score_computers as sc
+    g = torch.Generator(device=cuda).manual_seed(k)
+    y = torch.randn(3 * k, k, device=cuda, generator=g, dtype=torch.float64)
+    A = (y.T @ y / k).float()
+    lam = 1e-2
+    ref = torch.linalg.inv(A.double() + lam * torch.eye(k, device=cuda, dtype=torch.float64))
+    inv = sc.spd_inverse_(A.clone(), lam, rescale=False)
+    assert torch.equal(inv, inv.T)
+    assert rel(inv, ref) <= 2e-5, rel(inv, ref)
+    inv2 = sc.spd_inverse_(A.clone(), lam, rescale=True)
+    assert rel(inv2, ref / ref.abs().mean()) <= 2e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (129, 257, 33), (300, 700, 95), (128, 256, 64), (513, 100, 4097)])
+def test_gram_and_gemm_at_ragged_sizes(cuda, M, N, K):
+    """Tile, chunk (64 k) and slot (32 k) boundaries of both GEMM kernels, with accumulation into existing output."""
+    from trak_b200 import score_computers as sc
+    g = torch.Generator(device=cuda).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=cuda, generator=g)
+    b = torch.randn(N, K, device=cuda, generator=g)
+    out = torch.full((M, N), 2.0, device=cuda)
+    sc.gemm_nt(a, b, out=out, accumulate=True, alpha=-0.5)
+    assert rel(out, 2.0 - 0.5 * (a.double() @ b.double().T)) <= 3e-5   # one long tensor-core accumulation
+    x = torch.randn(K, N, device=cuda, generator=g)          # Gram over K rows: the chunked kernel
+    gram = torch.ones(N, N, device=cuda)
+    sc.gram(x, out=gram, accumulate=True)
+    want = 1.0 + x.double().T @ x.double()
+    assert torch.equal(gram, gram.T)
+    assert rel(gram, want) <= 1e-6
