@@ -388,83 +388,83 @@ gemm_nt_chunked_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     // 128 running sums + 64 values in flight).  Each role's code sits wholly inside its branch,
     // which is what lets the compiler allocate past the launch bound there.
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-      if (warp == 0 && lane == 0) {
-        // ------------------------------- TMA producer -------------------------------
-        prefetch_tmap(&map_a);
-        prefetch_tmap(&map_b);
-        uint32_t slot = 0, ph = 0;
-        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-            if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) {
-                gemm_fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, kb);
-                break;
-            }
-            const uint32_t bar = smem_u32(&bar_full[slot]);
-            const uint32_t sa = smem_base + slot * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
-            mbar_expect_tx(bar, CK_SLOT_BYTES);
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ------------------------------- TMA producer -------------------------------
+            prefetch_tmap(&map_a);
+            prefetch_tmap(&map_b);
+            uint32_t slot = 0, ph = 0;
+            for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                if (!mbar_wait(smem_u32(&bar_empty[slot]), ph ^ 1u, abort_flag)) {
+                    gemm_fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, kb);
+                    break;
+                }
+                const uint32_t bar = smem_u32(&bar_full[slot]);
+                const uint32_t sa = smem_base + slot * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+                mbar_expect_tx(bar, CK_SLOT_BYTES);
 #pragma unroll
-            for (uint32_t pl = 0; pl < 2; ++pl) {
-                tma_load_2d(sa + pl * GTILE_BYTES, &map_a, 0, (int)(((tile_m * p.kblocks + kb) * 2u + pl) * 128u), bar);
+                for (uint32_t pl = 0; pl < 2; ++pl) {
+                    tma_load_2d(sa + pl * GTILE_BYTES, &map_a, 0, (int)(((tile_m * p.kblocks + kb) * 2u + pl) * 128u), bar);
 #pragma unroll
-                for (uint32_t h = 0; h < 2; ++h)
-                    tma_load_2d(sb + (pl * 2u + h) * GTILE_BYTES, &map_b, 0,
-                                (int)((((tile_n * 2u + h) * p.kblocks + kb) * 2u + pl) * 128u), bar);
+                    for (uint32_t h = 0; h < 2; ++h)
+                        tma_load_2d(sb + (pl * 2u + h) * GTILE_BYTES, &map_b, 0,
+                                    (int)((((tile_n * 2u + h) * p.kblocks + kb) * 2u + pl) * 128u), bar);
+                }
+                if (++slot == CK_SLOTS) {
+                    slot = 0;
+                    ph ^= 1u;
+                }
             }
-            if (++slot == CK_SLOTS) {
-                slot = 0;
-                ph ^= 1u;
-            }
-        }
-    } else if (warp == 1) {
-        // -------------------------------- MMA issuer --------------------------------
-        // The whole warp runs the loop and one elected lane issues: with warp-uniform control flow the
-        // descriptors and addresses stay in uniform registers, which the MMA and commit instructions
-        // take directly (computed under a one-lane branch each would be moved there first).
-        const bool leader = elect_one();
-        uint32_t slot = 0, ph = 0;  // a chunk takes slots (slot, slot + 1); slot stays even, so no wrap inside one
-        bool ok = true;
-        for (uint32_t c = 0; c < nchunks && ok; ++c) {
-            const uint32_t set = c & 1u, use = c >> 1;
-            bool got = mbar_wait(smem_u32(&bar_acc_empty[set]), (use & 1u) ^ 1u, abort_flag);
-            if (!__all_sync(0xffffffffu, got)) {
-                if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x10000u + c);
-                break;
-            }
-            tc_fence_after();
-            const uint32_t d = tmem_base + set * 256u;
-            const uint32_t nkb = min(2u, p.kblocks - 2u * c);
-            // per 32-k slot: its small terms first, then its large ones, and the slot is released
-            for (uint32_t j = 0; j < nkb; ++j) {
-                got = mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag);
+        } else if (warp == 1) {
+            // -------------------------------- MMA issuer --------------------------------
+            // The whole warp runs the loop and one elected lane issues: with warp-uniform control flow the
+            // descriptors and addresses stay in uniform registers, which the MMA and commit instructions
+            // take directly (computed under a one-lane branch each would be moved there first).
+            const bool leader = elect_one();
+            uint32_t slot = 0, ph = 0;  // a chunk takes slots (slot, slot + 1); slot stays even, so no wrap inside one
+            bool ok = true;
+            for (uint32_t c = 0; c < nchunks && ok; ++c) {
+                const uint32_t set = c & 1u, use = c >> 1;
+                bool got = mbar_wait(smem_u32(&bar_acc_empty[set]), (use & 1u) ^ 1u, abort_flag);
                 if (!__all_sync(0xffffffffu, got)) {
-                    if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, 2u * c + j);
-                    ok = false;
+                    if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x10000u + c);
                     break;
                 }
                 tc_fence_after();
-                const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
-                const uint64_t a_hi = smem_desc_k_sw64(sa), a_lo = smem_desc_k_sw64(sa + GTILE_BYTES);
-                const uint64_t b_hi = smem_desc_k_sw64(sb), b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES);
-                if (leader) {
-#pragma unroll
-                    for (uint32_t kk = 0; kk < 2; ++kk) {
-                        umma_f16_ss(d, a_hi + 2u * kk, b_lo + 2u * kk, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
-                        umma_f16_ss(d, a_lo + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                const uint32_t d = tmem_base + set * 256u;
+                const uint32_t nkb = min(2u, p.kblocks - 2u * c);
+                // per 32-k slot: its small terms first, then its large ones, and the slot is released
+                for (uint32_t j = 0; j < nkb; ++j) {
+                    got = mbar_wait(smem_u32(&bar_full[slot + j]), ph, abort_flag);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        if (leader) gemm_fail(p.status, abort_flag, ST_TIMEOUT_FULL_B, 2u * c + j);
+                        ok = false;
+                        break;
                     }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + (slot + j) * CK_SLOT_BYTES, sb = sa + 2u * GTILE_BYTES;
+                    const uint64_t a_hi = smem_desc_k_sw64(sa), a_lo = smem_desc_k_sw64(sa + GTILE_BYTES);
+                    const uint64_t b_hi = smem_desc_k_sw64(sb), b_lo = smem_desc_k_sw64(sb + 2u * GTILE_BYTES);
+                    if (leader) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 2; ++kk) umma_f16_ss(d, a_hi + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
-                    tc_commit(smem_u32(&bar_empty[slot + j]));
+                        for (uint32_t kk = 0; kk < 2; ++kk) {
+                            umma_f16_ss(d, a_hi + 2u * kk, b_lo + 2u * kk, p.idesc, (j > 0 || kk > 0) ? 1u : 0u);
+                            umma_f16_ss(d, a_lo + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                        }
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 2; ++kk) umma_f16_ss(d, a_hi + 2u * kk, b_hi + 2u * kk, p.idesc, 1u);
+                        tc_commit(smem_u32(&bar_empty[slot + j]));
+                    }
+                }
+                if (!ok) break;
+                if (leader) tc_commit(smem_u32(&bar_acc_full[set]));
+                slot += nkb;
+                if (slot >= CK_SLOTS) {
+                    slot = 0;
+                    ph ^= 1u;
                 }
             }
-            if (!ok) break;
-            if (leader) tc_commit(smem_u32(&bar_acc_full[set]));
-            slot += nkb;
-            if (slot >= CK_SLOTS) {
-                slot = 0;
-                ph ^= 1u;
-            }
         }
-      }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------------- running sums, then the epilogue ----------------------
