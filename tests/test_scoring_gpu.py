@@ -222,3 +222,21 @@ def test_gram_and_gemm_at_ragged_sizes(cuda, M, N, K):
     want = 1.0 + x.double().T @ x.double()
     assert torch.equal(gram, gram.T)
     assert rel(gram, want) <= 1e-6
+
+
+def test_scores_stream_to_a_host_accumulator_in_several_blocks(cuda):
+    """The host accumulator path: more row blocks than staging buffers, a ragged last block, two calls
+    accumulating (two checkpoints), fp32 and fp16 accumulators."""
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m = 3000, 256, 70
+    F = torch.randn(n, k, generator=torch.Generator().manual_seed(1))
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(2))
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda)
+    sc.HOST_STAGE_BYTES = 256 * m * 4 * 3            # 768 rows per block: four blocks, the last one ragged
+    want = F.double() @ T.double().T
+    for dt, tol in ((torch.float32, 1e-5), (torch.float16, 2e-3)):
+        acc = torch.zeros(n, m, dtype=dt)
+        sc.get_scores(F, T, acc)
+        assert rel(acc, want) <= tol
+        sc.get_scores(F.to(cuda), T.to(cuda), acc)
+        assert rel(acc, 2 * want) <= tol

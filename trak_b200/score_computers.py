@@ -15,7 +15,8 @@ passed to an unmodified ``TRAKer(score_computer=B200ScoreComputer)``
   (one all-reduce of k x k fp32) -- rows sharded across GPUs, everything else
   local: the inverse is replicated, features and scores stay row-sharded;
 * ``get_scores`` takes an optional ``row_scale`` (the out-to-loss weights) that is
-  applied inside the GEMM epilogue.
+  applied inside the GEMM epilogue, and streams the scores to a host accumulator through
+  two pinned buffers while the next block is being multiplied.
 
 There is no CPU path: tensors are moved to ``device`` and the CUDA library must load.
 """
@@ -163,19 +164,59 @@ class B200ScoreComputer:
     # -- trak/score_computers.py:179-189
     def get_scores(self, features: torch.Tensor, target_grads: torch.Tensor, accumulator: torch.Tensor,
                    row_scale: torch.Tensor = None) -> None:
+        """``accumulator += features @ target_grads.T`` (times ``row_scale`` per train row when given).
+
+        TRAKer keeps the accumulator on the host (trak/traker.py:632): the product then leaves the GPU
+        through two pinned staging buffers of at most ``HOST_STAGE_BYTES`` each, the copy of one row block
+        overlapping the GEMM of the next and the host-side ``+=`` of the one before, instead of one
+        synchronous pageable copy per block."""
         targets = _as_device_matrix(target_grads, self.device)
+        m = targets.shape[0]
+        on_host = accumulator.device.type == "cpu"
+        step = self.CUDA_MAX_DIM_SIZE
+        if on_host:
+            step = max(256, min(step, self.HOST_STAGE_BYTES // (4 * m) // 256 * 256))
+            stage = self._host_stage(min(step, features.shape[0]), m)
+        pending = None
+
+        def flush(item):
+            rows, buf, event = item
+            event.synchronize()
+            accumulator[rows] += buf.to(accumulator.dtype)
+
         start = 0
-        for block in torch.split(features, self.CUDA_MAX_DIM_SIZE, dim=0):
+        for i, block in enumerate(torch.split(features, step, dim=0)):
             blk = _as_device_matrix(block, self.device)
             rs = None if row_scale is None else row_scale.reshape(-1)[start:start + blk.shape[0]]
             part = gemm_nt(blk, targets, row_scale=rs)
             rows = slice(start, start + blk.shape[0])
-            if accumulator.device == part.device:
-                accumulator[rows] += part.to(accumulator.dtype)
-            else:
-                accumulator[rows] += part.to(accumulator.dtype).to(accumulator.device)
             start += blk.shape[0]
+            if not on_host:
+                if accumulator.device == part.device:
+                    accumulator[rows] += part.to(accumulator.dtype)
+                else:
+                    accumulator[rows] += part.to(accumulator.dtype).to(accumulator.device)
+                continue
+            # buffer i % 2 was last read by the flush of block i - 2, which has returned
+            buf = stage[i % 2][:blk.shape[0]]
+            buf.copy_(part, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(self.device))
+            if pending is not None:
+                flush(pending)
+            pending = (rows, buf, event)
+        if pending is not None:
+            flush(pending)
         _lib.device_status(self.device.index)
+
+    HOST_STAGE_BYTES = 256 << 20  # each of the two pinned buffers get_scores copies through
+
+    def _host_stage(self, rows: int, m: int):
+        """Two pinned fp32 buffers [rows, m], kept between calls (pinning is slow) and regrown when too small."""
+        stage = getattr(self, "_stage", None)
+        if stage is None or stage[0].shape[0] < rows or stage[0].shape[1] != m:
+            self._stage = stage = [torch.empty(rows, m, dtype=torch.float32).pin_memory() for _ in range(2)]
+        return stage
 
 
 def reduce_gram(local_gram: torch.Tensor, process_group=None) -> torch.Tensor:
