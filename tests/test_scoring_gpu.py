@@ -240,3 +240,23 @@ def test_scores_stream_to_a_host_accumulator_in_several_blocks(cuda):
         assert rel(acc, want) <= tol
         sc.get_scores(F.to(cuda), T.to(cuda), acc)
         assert rel(acc, 2 * want) <= tol
+
+
+def test_scores_without_forming_the_features(cuda):
+    """get_scores_from_grads (targets through the inverse first, one product over the train rows) against
+    get_x_xtx_inv + get_scores and against the CPU port of the reference."""
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m, lam = 2500, 333, 77, 1e-2
+    X = torch.randn(n, k, generator=torch.Generator().manual_seed(4)) / k ** 0.5
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(5)) / k ** 0.5
+    w = torch.rand(n, 1, generator=torch.Generator().manual_seed(6))
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, CUDA_MAX_DIM_SIZE=1024, lambda_reg=lam)
+    gram = sc.get_xtx(X)
+    two_step = torch.zeros(n, m)
+    sc.get_scores(sc.get_x_xtx_inv(X, gram), T, two_step, row_scale=w)
+    direct = torch.zeros(n, m)
+    sc.get_scores_from_grads(X, gram, T, direct, row_scale=w)
+    assert rel(direct, two_step) <= 1e-4
+    s_ref = torch.zeros(n, m)
+    br.scores(br.x_xtx_inv(X, br.xtx(X), lam), T, s_ref)
+    assert rel(direct, br.finalize_scores_epilogue(s_ref, w, 1)) <= TOL

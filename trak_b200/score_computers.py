@@ -170,7 +170,22 @@ class B200ScoreComputer:
         through two pinned staging buffers of at most ``HOST_STAGE_BYTES`` each, the copy of one row block
         overlapping the GEMM of the next and the host-side ``+=`` of the one before, instead of one
         synchronous pageable copy per block."""
+        self._accumulate_products(features, _as_device_matrix(target_grads, self.device), accumulator, row_scale)
+
+    def get_scores_from_grads(self, grads: torch.Tensor, xtx: torch.Tensor, target_grads: torch.Tensor,
+                              accumulator: torch.Tensor, row_scale: torch.Tensor = None) -> None:
+        """The same scores without materialising the features:
+        ``accumulator += grads @ (inv @ target_grads.T)`` with ``inv`` the regularised, rescaled inverse of
+        ``xtx`` exactly as ``get_x_xtx_inv`` forms it (trak/score_computers.py:157-168).  One product over
+        the train rows instead of two: ``2 k^2 m`` flop for ``inv @ target_grads.T`` replace the ``2 n k^2``
+        of the features.  For callers that do not need the features themselves (TRAKer stores them)."""
+        inv = xtx.to(self.device, torch.float32).clone()
+        spd_inverse_(inv, self.lambda_reg, rescale=True)
         targets = _as_device_matrix(target_grads, self.device)
+        solved = gemm_nt(targets.float(), inv)  # [m, k] = target_grads @ inv  (inv is symmetric)
+        self._accumulate_products(grads, solved, accumulator, row_scale)
+
+    def _accumulate_products(self, features, targets, accumulator, row_scale):
         m = targets.shape[0]
         on_host = accumulator.device.type == "cpu"
         step = self.CUDA_MAX_DIM_SIZE
