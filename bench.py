@@ -12,7 +12,9 @@ no data-path collective (weak scaling).
 After the projection, one featurize step of the CIFAR ResNet-18 configuration (key ``featurize``:
 torch.func gradients -> projection from the gradient dict) and the second hot path are measured
 too (key ``scoring`` of the same line): the whole C4 scoring job -- X fp32 [1,000,000 x 8192] sharded by rows over the GPUs,
-Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000 targets.
+Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000 targets (the
+reference's ordering; ``scoring.without_features`` times the same scores with the targets taken
+through the inverse first, which never forms the features).
 
 Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
 HBM; ``e2e`` is the same through the public ``trak_b200.fast_jl.project`` call with every
