@@ -65,95 +65,156 @@ __global__ void add_diag_kernel(float* A, int64_t lda, int k, float lambda) {
 
 // Factors the jb x jb diagonal block A = L L^T and inverts L in the same sweep; writes L back over the
 // lower triangle and inv(L) (lower, zero above, zero-padded to 64 x 64) to dinv.  256 threads as a
-// 16 x 16 grid, each keeping a 4 x 4 piece of the block and of the inverse in registers.  Column c:
-// the owners publish the current column c of the block and row c of the inverse in shared memory,
-// one barrier, then every thread applies the rank-one updates
-//     S[i][j] -= S[i][c] S[j][c] / pivot   (i, j > c),     W[i][:] -= S[i][c] W[c][:] / pivot   (i > c)
-// (the second is forward elimination of [L | I]) with r = 1/sqrt(pivot) folded into both factors and
-// the operands of rows and columns <= c replaced by zero, so the sixteen multiply-adds of a piece need
-// no predicates.  Column c of the block and row c of the inverse are final after step c up to the
-// factor r, which is kept per column and applied once at the end.  The buffers alternate between
-// columns, so one barrier per column is enough.  Rows and columns beyond jb are an identity block.
-// `buf` is 5 * 64 floats of shared memory, `bad` one shared int.
+// 16 x 16 grid, thread (ty, tx) keeping the 4 x 4 piece S[4 ty.., 4 tx..] of the block and the same piece
+// of W (which starts as the identity and ends as inv(L): forward elimination of [L | I]) in registers.
+// The block is walked four columns at a time, two barriers per step instead of two per column (a
+// column-by-column sweep spent 1000 cycles per column, almost all of it waiting: 33 us per block):
+//   1. the thread on the diagonal publishes its 4 x 4 piece D;
+//   2. every thread of piece column q factors D = Ld Ld^T itself (a few dozen operations), turns its
+//      piece into the matching rows of L (B Ld^-T) and publishes them; every thread of piece row q
+//      applies Ld^-1 to its four rows of W, which makes them final, and publishes them;
+//   3. the threads below apply the rank-four updates  S -= L_q L_q^T  (pieces right of column q)
+//      and  W -= L_q W_q  (pieces up to column q; W_q is zero beyond).
+// Rows and columns beyond jb are an identity block.  `buf` is 16 + 2 * 256 floats of shared memory.
+struct Chol4 {
+    float l10, l20, l30, l21, l31, l32;  // strictly lower part of Ld
+    float r0, r1, r2, r3;                // reciprocals of its diagonal
+    float d0, d1, d2, d3;                // its diagonal
+    bool ok;
+};
+__device__ __forceinline__ float rsqrt_newton(float d) {
+    float r = rsqrtf(d);
+    return r * (1.5f - 0.5f * d * r * r);
+}
+__device__ __forceinline__ Chol4 chol4(const float* D) {  // D: 4 x 4 row-major, lower part used
+    Chol4 c;
+    c.ok = true;
+    float p = D[0];
+    c.ok = c.ok && p > 0.0f;
+    c.r0 = rsqrt_newton(p);
+    c.d0 = p * c.r0;
+    c.l10 = D[4] * c.r0;
+    c.l20 = D[8] * c.r0;
+    c.l30 = D[12] * c.r0;
+    p = fmaf(-c.l10, c.l10, D[5]);
+    c.ok = c.ok && p > 0.0f;
+    c.r1 = rsqrt_newton(p);
+    c.d1 = p * c.r1;
+    c.l21 = fmaf(-c.l20, c.l10, D[9]) * c.r1;
+    c.l31 = fmaf(-c.l30, c.l10, D[13]) * c.r1;
+    p = fmaf(-c.l21, c.l21, fmaf(-c.l20, c.l20, D[10]));
+    c.ok = c.ok && p > 0.0f;
+    c.r2 = rsqrt_newton(p);
+    c.d2 = p * c.r2;
+    c.l32 = fmaf(-c.l31, c.l21, fmaf(-c.l30, c.l20, D[14])) * c.r2;
+    p = fmaf(-c.l32, c.l32, fmaf(-c.l31, c.l31, fmaf(-c.l30, c.l30, D[15])));
+    c.ok = c.ok && p > 0.0f;
+    c.r3 = rsqrt_newton(p);
+    c.d3 = p * c.r3;
+    return c;
+}
+// x <- Ld^-1 x for one column of four values (forward substitution)
+__device__ __forceinline__ void solve4(const Chol4& c, float& x0, float& x1, float& x2, float& x3) {
+    x0 = x0 * c.r0;
+    x1 = fmaf(-c.l10, x0, x1) * c.r1;
+    x2 = fmaf(-c.l21, x1, fmaf(-c.l20, x0, x2)) * c.r2;
+    x3 = fmaf(-c.l32, x2, fmaf(-c.l31, x1, fmaf(-c.l30, x0, x3))) * c.r3;
+}
 __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t* status, float* buf, int* bad) {
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-    float (*colbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf);
-    float (*rowbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf + 2 * NB);
-    float* rscale = buf + 4 * NB;
+    float* diagbuf = buf;                                                  // [4][4]
+    float (*colbuf)[4] = reinterpret_cast<float(*)[4]>(buf + 16);          // [64][4]: rows of L_q
+    float (*rowbuf)[NB] = reinterpret_cast<float(*)[NB]>(buf + 16 + 256);  // [4][64]: rows of W_q
     float sblk[4][4], wblk[4][4];
     if (tid == 0) *bad = 0;
-    if (tid < NB) rscale[tid] = 1.0f;
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const int i = ty * 4 + a, j = tx * 4 + b;
-            sblk[a][b] = (i < jb && j <= i) ? A[(int64_t)i * lda + j] : (i == j ? 1.0f : 0.0f);
+            // the diagonal pieces hold both triangles (symmetric), the others only what lies below
+            const bool in = i < jb && j < jb && (j <= i || tx == ty);
+            sblk[a][b] = in ? A[(int64_t)(j <= i ? i : j) * lda + (j <= i ? j : i)] : (i == j ? 1.0f : 0.0f);
             wblk[a][b] = i == j ? 1.0f : 0.0f;
         }
-    for (int c = 0; c < jb; ++c) {
-        const int pb = c & 1, cq = c >> 2, cr = c & 3;
-        if (tx == cq) {
+    const int steps = (jb + 3) >> 2;
+    for (int q = 0; q < steps; ++q) {
+        if (ty == q && tx == q) {
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                float v = sblk[a][0];
-                if (cr == 1) v = sblk[a][1];
-                if (cr == 2) v = sblk[a][2];
-                if (cr == 3) v = sblk[a][3];
-                colbuf[pb][ty * 4 + a] = v;
-            }
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) diagbuf[a * 4 + b] = sblk[a][b];
         }
-        if (ty == cq) {
+        __syncthreads();
+        if (tx == q || ty == q) {
+            const Chol4 c = chol4(diagbuf);
+            if (ty == q && tx == q && !c.ok) *bad = 1;
+            if (tx == q && ty >= q) {
+                if (ty == q) {  // the diagonal piece becomes Ld
+                    sblk[0][0] = c.d0;
+                    sblk[1][0] = c.l10; sblk[1][1] = c.d1;
+                    sblk[2][0] = c.l20; sblk[2][1] = c.l21; sblk[2][2] = c.d2;
+                    sblk[3][0] = c.l30; sblk[3][1] = c.l31; sblk[3][2] = c.l32; sblk[3][3] = c.d3;
+                    sblk[0][1] = sblk[0][2] = sblk[0][3] = sblk[1][2] = sblk[1][3] = sblk[2][3] = 0.0f;
+                } else {        // rows of L below it: B Ld^-T, i.e. Ld^-1 applied along each row
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                float v = wblk[0][b];
-                if (cr == 1) v = wblk[1][b];
-                if (cr == 2) v = wblk[2][b];
-                if (cr == 3) v = wblk[3][b];
-                rowbuf[pb][tx * 4 + b] = v;
+                    for (int a = 0; a < 4; ++a) solve4(c, sblk[a][0], sblk[a][1], sblk[a][2], sblk[a][3]);
+                }
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+                    *reinterpret_cast<float4*>(colbuf[ty * 4 + a]) =
+                        make_float4(sblk[a][0], sblk[a][1], sblk[a][2], sblk[a][3]);
+            }
+            if (ty == q) {      // four rows of W become final: Ld^-1 applied down each column
+#pragma unroll
+                for (int b = 0; b < 4; ++b) solve4(c, wblk[0][b], wblk[1][b], wblk[2][b], wblk[3][b]);
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+                    *reinterpret_cast<float4*>(&rowbuf[a][tx * 4]) =
+                        make_float4(wblk[a][0], wblk[a][1], wblk[a][2], wblk[a][3]);
             }
         }
         __syncthreads();
-        const float d = colbuf[pb][c];
-        // 1/sqrt(pivot): hardware estimate and one Newton step
-        float r = rsqrtf(d);
-        r = r * (1.5f - 0.5f * d * r * r);
-        if (tid == 0) {
-            if (!(d > 0.0f)) *bad = 1;
-            rscale[c] = r;
-        }
-        if (ty * 4 + 3 <= c) continue;  // none of this thread's rows lies below row c
-        float li[4];
+        if (ty > q) {
+            float li[4][4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) li[a] = ty * 4 + a > c ? colbuf[pb][ty * 4 + a] * r : 0.0f;
-        if (tx * 4 + 3 > c) {  // columns beyond c: the block itself
-            float lj[4];
+            for (int a = 0; a < 4; ++a) {
+                const float4 v = *reinterpret_cast<const float4*>(colbuf[ty * 4 + a]);
+                li[a][0] = v.x; li[a][1] = v.y; li[a][2] = v.z; li[a][3] = v.w;
+            }
+            if (tx > q && tx <= ty) {
 #pragma unroll
-            for (int b = 0; b < 4; ++b) lj[b] = tx * 4 + b > c ? colbuf[pb][tx * 4 + b] * r : 0.0f;
+                for (int b = 0; b < 4; ++b) {
+                    const float4 v = *reinterpret_cast<const float4*>(colbuf[tx * 4 + b]);
 #pragma unroll
-            for (int a = 0; a < 4; ++a)
+                    for (int a = 0; a < 4; ++a)
+                        sblk[a][b] = fmaf(-li[a][3], v.w, fmaf(-li[a][2], v.z, fmaf(-li[a][1], v.y,
+                                          fmaf(-li[a][0], v.x, sblk[a][b]))));
+                }
+            }
+            if (tx <= q) {
 #pragma unroll
-                for (int b = 0; b < 4; ++b) sblk[a][b] = fmaf(-li[a], lj[b], sblk[a][b]);
-        }
-        if (tx * 4 <= c) {  // columns up to c: the inverse (its row c is zero beyond column c)
-            float wr[4];
+                for (int cc = 0; cc < 4; ++cc) {
+                    const float4 v = *reinterpret_cast<const float4*>(&rowbuf[cc][tx * 4]);
 #pragma unroll
-            for (int b = 0; b < 4; ++b) wr[b] = rowbuf[pb][tx * 4 + b] * r;
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) wblk[a][b] = fmaf(-li[a], wr[b], wblk[a][b]);
+                    for (int a = 0; a < 4; ++a) {
+                        wblk[a][0] = fmaf(-li[a][cc], v.x, wblk[a][0]);
+                        wblk[a][1] = fmaf(-li[a][cc], v.y, wblk[a][1]);
+                        wblk[a][2] = fmaf(-li[a][cc], v.z, wblk[a][2]);
+                        wblk[a][3] = fmaf(-li[a][cc], v.w, wblk[a][3]);
+                    }
+                }
+            }
         }
     }
-    __syncthreads();
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const int i = ty * 4 + a, j = tx * 4 + b;
             const bool in = i < jb && j <= i;
-            if (in) A[(int64_t)i * lda + j] = sblk[a][b] * rscale[j];
-            dinv[i * NB + j] = in ? wblk[a][b] * rscale[i] : 0.0f;
+            if (in) A[(int64_t)i * lda + j] = sblk[a][b];
+            dinv[i * NB + j] = in ? wblk[a][b] : 0.0f;
         }
     __syncthreads();
     if (tid == 0 && *bad) atomicCAS(status, 0u, (uint32_t)ST_NOT_SPD);
@@ -161,7 +222,7 @@ __device__ void chol_block(float* A, int64_t lda, int jb, float* dinv, uint32_t*
 
 __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, int jb, float* dinv,
                                                         uint32_t* status) {
-    __shared__ float buf[5 * NB];
+    __shared__ __align__(16) float buf[16 + 2 * 256];
     __shared__ int bad;
     chol_block(A, lda, jb, dinv, status, buf, &bad);
 }
