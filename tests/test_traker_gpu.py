@@ -53,10 +53,10 @@ def _model_and_data(cuda):
     return model, train, targets
 
 
-def _run(trak, model, train, targets, save_dir, **kw):
+def _run(trak, model, train, targets, save_dir, half=False, **kw):
     n, m = train[0].shape[0], targets[0].shape[0]
     tr = trak.TRAKer(model=model, task="image_classification", train_set_size=n, save_dir=str(save_dir),
-                     device="cuda", proj_dim=1024, use_half_precision=False, lambda_reg=0.0,
+                     device="cuda", proj_dim=1024, use_half_precision=half, lambda_reg=0.0,
                      logging_level=40, **kw)
     ckpt = model.state_dict()
     tr.load_checkpoint(ckpt, model_id=0)
@@ -117,3 +117,27 @@ def test_unmodified_traker_runs_on_the_shim_and_on_the_mirrored_classes(trak, cu
     flat = trak.utils.vectorize(grads, device="cuda").float().cpu().numpy()
     ref = o.project(o.RADEMACHER, flat, 1024, 0, tr_a.projector.num_sms, round_f16=True) / D ** 0.5
     assert np.linalg.norm(g_a[:200] - ref) <= 1e-3 * np.linalg.norm(ref)
+
+
+def test_unmodified_traker_in_its_default_half_precision(trak, cuda, tmp_path):
+    """TRAKer's default: projections, Gram, features and scores stored and handed over in fp16
+    (trak/traker.py:141).  The mirrored classes must take that as they take fp32; against the fp32 run the
+    scores differ by what fp16 storage of the features costs."""
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    from trak_b200.score_computers import B200ScoreComputer
+    model, train, targets = _model_and_data(cuda)
+    D = sum(p.numel() for p in model.parameters())
+
+    def projector():
+        return CudaProjector(grad_dim=D, proj_dim=1024, seed=0, proj_type=ProjectionType.rademacher,
+                             device=cuda, max_batch_size=32)
+
+    _, s32, _, _ = _run(trak, model, train, targets, tmp_path / "f32", projector=projector(),
+                        score_computer=B200ScoreComputer)
+    tr16, s16, g16, _ = _run(trak, model, train, targets, tmp_path / "f16", half=True, projector=projector(),
+                             score_computer=B200ScoreComputer)
+    assert g16.dtype == np.float16 and tr16.score_computer.dtype == torch.float16
+    assert np.isfinite(s16).all()
+    err = np.linalg.norm(s16.astype(np.float64) - s32) / np.linalg.norm(s32)
+    print(f"half-precision TRAKer against the fp32 run: {err:.2e}")
+    assert err <= 5e-2, err
