@@ -16,6 +16,15 @@ Gram + one all-reduce + Cholesky inverse + features + weighted scores for 10,000
 reference's ordering; ``scoring.without_features`` times the same scores with the targets taken
 through the inverse first, which never forms the features).
 
+Further keys of the same line: ``rademacher`` (the same shape with the Rademacher matrix), ``rows_sweep``
+(16 ... 512 rows per call, both matrix types: what one GPU does when the 128-row batch is split over 8 ... 1
+GPUs, and what larger batches gain), ``scaling_strong`` (N > 1: the 128-row batch split 128/N rows per rank),
+``scoring.e2e`` (the three score-computer calls as TRAKer makes them, train rows in pinned host memory, scores
+into a host accumulator), ``scoring.parity`` (this library against the reference's CPU class at k = 8192),
+``scoring.multi_gpu_check`` (N > 1: rank 0 recomputes a block of scores alone), ``featurize_job`` (the whole
+50,000-example featurize job with its stores) and ``chunked`` (GPT-2-small per-sample gradients through the
+chunked projector).
+
 Prints ONE JSON line (rank 0).  ``value`` is examples/s with the batch resident in
 HBM; ``e2e`` is the same through the public ``trak_b200.fast_jl.project`` call with every
 step's batch copied from pinned host memory and its result read back (the copy of the next
@@ -48,10 +57,10 @@ SEED = 17
 TILES = 148
 BLOCK = 100  # BasicProjector's column block (trak/projectors.py:229)
 
-# DRAM traffic of one projection-kernel launch on the full workload, from the ncu
-# capture summarised in profiles/project_kernel_normal_small.md (dram__bytes_read.sum +
-# dram__bytes_write.sum at D/10, which grows in proportion to D, times 10)
-NCU_TRAFFIC_BYTES_FULL = 3.51e9
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the three launches of one projection call on
+# the full workload, from the ncu capture summarised in profiles/project_kernel_normal_bench.md: taken at D/10
+# (traffic grows in proportion to D) and multiplied by 10.
+NCU_TRAFFIC_BYTES_FULL = {"stage_kernel": 5.73e9, "project_kernel": 3.51e9, "reduce_kernel": 0.08e9}
 
 
 def measured_peaks():
@@ -61,6 +70,15 @@ def measured_peaks():
             d = json.load(f)
         return float(d.get("bf16_tflops_sustained", d.get("bf16_tflops"))), "measured (sustained bf16, MEASURED_PEAKS.json)"
     return 1400.0, "fallback (sustained bf16 figure of an earlier measurement on this pool)"
+
+
+def burst_peak():
+    """The bf16 GEMM rate of a kernel timed alone (MEASURED_PEAKS.json), else this pool's earlier figure."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f).get("bf16_tflops", 1590.0))
+    return 1590.0
 
 
 class ClockSampler:
@@ -208,22 +226,27 @@ def run_reference(args, D):
         return
     import torch
     threads = os.cpu_count() or 1
-    blocks = 2
+    blocks = 1   # one of the 41 column blocks per step keeps a --steps 20 --warmup 5 run within minutes
     nblocks = -(-K_DIM // BLOCK)
     for _ in range(args.warmup):
         cpu_port_sample(ROWS, D, threads, blocks)
-    full = []
+    full, measured = [], []
     for _ in range(args.steps):
-        s, _ = cpu_port_sample(ROWS, D, threads, blocks)
+        s, m = cpu_port_sample(ROWS, D, threads, blocks)
         full.append(s)
+        measured.append(m)
     sec = sum(full) / len(full)
     value = ROWS / sec
     who = "the reference's unmodified BasicProjector" if cpu_kind() == "reference" else "CPU port of BasicProjector"
     sample = (f"{who}: each step projects all {ROWS} rows x D={D} onto {blocks} of {nblocks} column blocks of "
-              f"{BLOCK} (matrix block generated + matmul), time scaled by {nblocks}/{blocks}")
+              f"{BLOCK} (matrix block generated + matmul); value = rows / (measured step time x {nblocks}/{blocks})")
     line = {
         "impl": "reference", "metric": "jl_projected_examples_per_s", "value": value, "unit": "examples/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        # the time one timed step actually took (a bounded sample: `sampled` of the column blocks);
+        # `extrapolated_ms_per_step` is that time scaled to all blocks, which is what `value` is computed from
+        "ms_per_step": sum(measured) / len(measured) * 1e3, "measured_ms_per_step": sum(measured) / len(measured) * 1e3,
+        "extrapolated_ms_per_step": sec * 1e3, "sampled": f"{blocks}/{nblocks}",
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(D),
         "cpu_baseline": {"value": value, "unit": "examples/s", "cores": torch.get_num_threads(),
@@ -271,12 +294,12 @@ def run_scoring(args, dev, rank, world, scale):
     scores = torch.empty(n, m, device=dev)
     feats = torch.empty(min(SC_BLOCK, n), k, device=dev)
     gram = torch.empty(k, k, device=dev)
+    group = dist.group.WORLD if world > 1 else None
 
     def job():
         for i in range(0, n, SC_BLOCK):
             sc.gram(X[i:i + SC_BLOCK], out=gram, accumulate=i > 0)
-        if world > 1:
-            dist.all_reduce(gram)
+        sc.reduce_gram(gram, group)                     # the one exchange of the path (NCCL all-reduce)
         sc.spd_inverse_(gram, SC_LAMBDA, rescale=True)  # gram now holds the rescaled inverse
         for i in range(0, n, SC_BLOCK):
             rows = min(SC_BLOCK, n - i)
@@ -289,8 +312,7 @@ def run_scoring(args, dev, rank, world, scale):
         # the same scores without the features: targets through the inverse first, one product over the rows
         for i in range(0, n, SC_BLOCK):
             sc.gram(X[i:i + SC_BLOCK], out=gram, accumulate=i > 0)
-        if world > 1:
-            dist.all_reduce(gram)
+        sc.reduce_gram(gram, group)
         sc.spd_inverse_(gram, SC_LAMBDA, rescale=True)
         sc.gemm_nt(T, gram, out=solved)
         for i in range(0, n, SC_BLOCK):
@@ -332,6 +354,7 @@ def run_scoring(args, dev, rank, world, scale):
            "algorithmic_tflops": scoring_flop(n_total, k, m) / sec / 1e12,
            "roofline": {"bound": "tensor", "achieved": scoring_flop(n_total, k, m) / sec / 1e12 / world, "peak": peak,
                         "unit": "TFLOP/s", "frac": scoring_flop(n_total, k, m) / sec / 1e12 / world / peak,
+                        "frac_burst": scoring_flop(n_total, k, m) / sec / 1e12 / world / burst_peak(),
                         "note": "fp32 inputs run as fp16 hi/lo splits: three tensor-core passes per algorithmic flop, "
                                 "so 1/3 of the bf16 peak is the ceiling of this figure"},
            "without_features": {"value": sec_direct, "unit": "s",
@@ -339,13 +362,86 @@ def run_scoring(args, dev, rank, world, scale):
                                             "never formed (2 k^2 m flop replace 2 n k^2)",
                                 "algorithmic_tflops": flop_direct / sec_direct / 1e12,
                                 "relative_difference_of_scores": direct_err}}
-    del X, scores, feats
+    if world > 1:
+        # Correctness of the sharded job: rank 0 alone regenerates every rank's shard (same seeds), forms the whole
+        # Gram by itself, inverts it and recomputes its first 256 rows of scores; the sharded job's all-reduce adds
+        # the same partial Grams in another order, so the two agree to fp32 round-off.
+        x256, w256 = X[:256].clone(), w[:256].clone()
+        del X, feats
+        torch.cuda.empty_cache()
+        if rank == 0:
+            g1 = torch.empty(k, k, device=dev)
+            first = True
+            for r in range(world):
+                lo_r, hi_r = sc.shard_rows(n_total, r, world)
+                gen_r = torch.Generator(device=dev).manual_seed(2000 + r)
+                for i in range(0, hi_r - lo_r, SC_BLOCK):
+                    blk = torch.randn(min(SC_BLOCK, hi_r - lo_r - i), k, device=dev, generator=gen_r) / k ** 0.5
+                    sc.gram(blk, out=g1, accumulate=not first)
+                    first = False
+            sc.spd_inverse_(g1, SC_LAMBDA, rescale=True)
+            alone = sc.gemm_nt(x256, sc.gemm_nt(T, g1), row_scale=w256)
+            out["multi_gpu_check"] = {
+                "rows": 256, "relative_difference": float((scores[:256] - alone).norm() / alone.norm()),
+                "what": f"rank 0's first 256 rows of scores from the {world}-GPU job (Gram summed by NCCL through "
+                        "score_computers.reduce_gram) against the same rows recomputed by rank 0 alone from all shards"}
+        dist.barrier()
+    else:
+        del X, feats
+    del scores
     torch.cuda.empty_cache()
     return out
 
 
-def scoring_cpu_baseline(threads):
-    """CPU port of BasicScoreComputer on a bounded sample (k full, fewer rows and targets), scaled to C4."""
+def run_scoring_e2e(dev, rank, world):
+    """The scoring path as TRAKer drives it (trak/traker.py:480-486, 632, 662-667): the train rows of this rank in
+    pinned HOST memory, B200ScoreComputer.get_xtx -> get_x_xtx_inv -> get_scores with a host accumulator.  Every
+    byte of X crosses PCIe twice (Gram, features), the features come back once and go in once more, and the scores
+    leave through the pinned staging pair and are added into the accumulator on the host."""
+    import torch
+    import torch.distributed as dist
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m = 131_072, SC_K, SC_M
+    X = torch.empty(n, k).pin_memory()
+    gen = torch.Generator(device=dev).manual_seed(2000 + rank)
+    for i in range(0, n, SC_BLOCK):
+        X[i:i + SC_BLOCK].copy_(torch.randn(min(SC_BLOCK, n - i), k, device=dev, generator=gen) / k ** 0.5)
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(3000)) / k ** 0.5
+    acc = torch.zeros(n, m).pin_memory()
+    sc = B200ScoreComputer(torch.float32, dev, lambda_reg=SC_LAMBDA,
+                           process_group=dist.group.WORLD if world > 1 else None)
+
+    def job():
+        gram = sc.get_xtx(X)
+        feats = sc.get_x_xtx_inv(X, gram)
+        sc.get_scores(feats, T, acc)
+
+    job()  # warms the pinned staging and the workspaces
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    job()
+    torch.cuda.synchronize()
+    sec = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+    sec = sec.item()
+    flop = scoring_flop(n * world, k, m)
+    out = {"value": sec, "unit": "s", "rows_per_gpu": n, "targets": m,
+           "h2d_bytes": 2 * n * k * 4 + m * k * 4, "d2h_bytes": n * m * 4,
+           "algorithmic_tflops": flop / sec / 1e12,
+           "rows_per_s": n * world / sec,
+           "what": "B200ScoreComputer.get_xtx / get_x_xtx_inv / get_scores, X in pinned host memory, features kept on "
+                   "the device as the reference does, scores added into a host accumulator (wall clock, max over ranks); "
+                   f"the full job is {SC_N // n // world} such shards per GPU"}
+    del X, acc
+    return out
+
+
+def scoring_cpu_baseline(threads, dev=None):
+    """The reference's BasicScoreComputer on the host cores on a bounded sample (k full, fewer rows and targets),
+    scaled to C4 -- and, with `dev`, this library on the very same sample, compared with it (``parity``)."""
     import torch
     from oracle import basic_ref
     torch.set_num_threads(threads)
@@ -361,10 +457,11 @@ def scoring_cpu_baseline(threads):
         xtx = basic_ref.xtx
         x_xtx_inv = lambda x, g: basic_ref.x_xtx_inv(x, g, SC_LAMBDA)  # noqa: E731
         scores = basic_ref.scores
+    ridge = (SC_N / n - 1) * torch.eye(k)  # keeps the sample as well conditioned as the full job's Gram
     t0 = time.perf_counter()
     g = xtx(X)
     t1 = time.perf_counter()
-    f = x_xtx_inv(X, g + (SC_N / n - 1) * torch.eye(k))  # keep the sample well conditioned
+    f = x_xtx_inv(X, g + ridge)
     t2 = time.perf_counter()
     acc = torch.zeros(n, m)
     scores(f, T, acc)
@@ -376,10 +473,27 @@ def scoring_cpu_baseline(threads):
     t_inv = time.perf_counter() - t4
     full = (t1 - t0) * SC_N / n + t_inv + max(0.0, (t2 - t1) - t_inv) * SC_N / n + (t3 - t2) * (SC_N / n) * (SC_M / m)
     who = "the reference's unmodified BasicScoreComputer" if trak is not None else "CPU port of BasicScoreComputer"
-    return {"value": full, "unit": "s", "cores": torch.get_num_threads(), "kind": cpu_kind(),
-            "sample": f"{who} at k={k} on {n} rows x {m} targets "
-                      f"(gram {t1 - t0:.1f} s, inverse {t_inv:.1f} s, features {t2 - t1 - t_inv:.1f} s, scores {t3 - t2:.1f} s), "
-                      f"Gram/features scaled by n, scores by n*m, inverse counted once"}
+    out = {"value": full, "unit": "s", "cores": torch.get_num_threads(), "kind": cpu_kind(),
+           "sample": f"{who} at k={k} on {n} rows x {m} targets "
+                     f"(gram {t1 - t0:.1f} s, inverse {t_inv:.1f} s, features {t2 - t1 - t_inv:.1f} s, scores {t3 - t2:.1f} s), "
+                     f"Gram/features scaled by n, scores by n*m, inverse counted once"}
+    parity = None
+    if dev is not None:
+        from trak_b200.score_computers import B200ScoreComputer
+        mine = B200ScoreComputer(torch.float32, dev, lambda_reg=SC_LAMBDA)
+        g_m = mine.get_xtx(X)
+        f_m = mine.get_x_xtx_inv(X, g_m + ridge.to(dev))
+        acc_m = torch.zeros(n, m)
+        mine.get_scores(f_m, T, acc_m)
+
+        def rel(a, b):
+            a, b = a.double().cpu(), b.double().cpu()
+            return float((a - b).norm() / b.norm())
+
+        parity = {"gram": rel(g_m, g), "features": rel(f_m, f), "scores": rel(acc_m, acc), "tolerance": 1e-3,
+                  "what": f"Frobenius-relative difference of this library from {who} on that sample "
+                          f"(k={k}, {n} rows, {m} targets, lambda {SC_LAMBDA})"}
+    return out, parity
 
 
 # ---- end-to-end featurize step (per-sample gradients -> projection) ------------------------------
@@ -459,6 +573,228 @@ def run_featurize(dev, rank, world):
             "config": {"workload": f"CIFAR ResNet-18 ({D} parameters, 62 tensors, fp32), batch {B} per GPU, "
                                    f"vmap(grad) margins -> Rademacher k={N}, host images in, host features out"},
             "ms_per_step": sec.item() * 1e3, "gradients_ms": g_ms / steps, "projection_ms": p_ms / steps}
+
+
+def time_projection(lib, fast_jl, g, ptype, calls=3, warm=1):
+    """(ms per call, ms of the projection kernel alone) of fast_jl.project on a resident batch: CUDA events
+    around the calls on the current stream, and the library's own event pair around the dominant kernel."""
+    import torch
+    out = torch.empty(g.shape[0], K_DIM, device=g.device, dtype=torch.float32)
+    for _ in range(warm):
+        fast_jl.project(g, K_DIM, SEED, TILES, ptype, out=out, strict=False)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(calls)]
+    for a, b in kev:
+        a.record()
+        b.record()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for a, b in kev:
+        lib.tb_profile_events(a.cuda_event, b.cuda_event)
+        fast_jl.project(g, K_DIM, SEED, TILES, ptype, out=out, strict=False)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / calls, sum(a.elapsed_time(b) for a, b in kev) / calls
+
+
+def run_rows_sweep(lib, fast_jl, _lib, dev, D, rows_list=(16, 32, 64, 128, 256, 512)):
+    """ms per call and examples/s of one GPU for batches of 16 ... 512 rows of the C2 gradients, both matrix
+    types.  16 / 32 / 64 rows are what one GPU gets when the 128-row batch is split over 8 / 4 / 2 GPUs; 256 and
+    512 rows show what one generation of the matrix serving more rows gains.  A batch of more than 256 rows is
+    one launch for the Gaussian matrix and 256-row passes for the Rademacher matrix."""
+    import torch
+    peak, _ = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    big = torch.empty(max(rows_list), D, device=dev, dtype=torch.float16)
+    for i in range(0, big.shape[0], 64):  # generated block-wise to bound temporary memory
+        big[i:i + 64] = (torch.randn(min(64, big.shape[0] - i), D, device=dev, generator=gen) * 1e-2).half()
+    out = {"rows": list(rows_list), "unit_ms": "ms per call (restage + project + reduce)", "proj_dim": K_DIM, "grad_dim": D}
+    for name, ptype in (("normal", _lib.TB_NORMAL), ("rademacher", _lib.TB_RADEMACHER)):
+        ms, eps, frac = [], [], []
+        for r in rows_list:
+            t, _ = time_projection(lib, fast_jl, big[:r], ptype)
+            ms.append(round(t, 3))
+            eps.append(round(r / t * 1e3, 1))
+            frac.append(round(2.0 * r * D * K_DIM / (t * 1e-3) / 1e12 / peak, 4))
+        out[name] = {"ms": ms, "examples_per_s": eps, "frac_of_sustained_peak": frac}
+    _lib.device_status(dev.index)
+    del big
+    fast_jl.free_workspaces()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_scaling_strong(lib, fast_jl, _lib, g, rank, world):
+    """The 128-row batch of the configuration split over the ranks (128 / N rows each, same virtual matrix, no
+    collective): examples/s = 128 / (slowest rank's time per call)."""
+    import torch
+    import torch.distributed as dist
+    rows = max(1, ROWS // world)
+    res = {"rows_per_gpu": rows, "scaling": "strong"}
+    for name, ptype in (("normal", _lib.TB_NORMAL), ("rademacher", _lib.TB_RADEMACHER)):
+        part = g[rank * rows % ROWS: rank * rows % ROWS + rows]
+        dist.barrier()
+        t, _ = time_projection(lib, fast_jl, part, ptype, calls=5, warm=2)
+        tt = torch.tensor([t], device=g.device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        res[name] = {"ms_per_call": tt.item(), "examples_per_s": rows * world / tt.item() * 1e3}
+    res["note"] = ("every rank regenerates the whole D x k matrix for its rows, as the reference does per 32 rows "
+                   "(fast_jl/fast_jl.cu:51): the Gaussian time does not fall with the rows per GPU")
+    return res
+
+
+def _cifar_resnet18(dev):
+    import torch
+    import torchvision
+    torch.manual_seed(0)
+    model = torchvision.models.resnet18(num_classes=10)
+    model.conv1 = torch.nn.Conv2d(3, 64, 3, 1, 1, bias=False)
+    model.maxpool = torch.nn.Identity()
+    return model.to(dev).eval()
+
+
+def run_featurize_job(dev, rank, world, total=50_000, batch=256):
+    """The whole featurize job of the CIFAR ResNet-18 configuration: `total` synthetic images (uniform pixels and
+    labels) sharded contiguously over the ranks, per-example margin gradients from torch.func, Rademacher
+    projection to k = 2048 with 1/sqrt(D) folded in, margin out-to-loss weights from a second forward
+    (trak/modelout_functions.py:153-179), both written into this rank's grads / out_to_loss stores (fp16 npy
+    memmaps, the reference's default dtype) through FeatureWriter.  Wall clock from the first batch to the
+    flushed stores, max over ranks."""
+    import shutil
+    import tempfile
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from torch.func import functional_call, grad, vmap
+    from trak_b200 import fast_jl, mmap_io
+    from trak_b200.featurize import FeatureWriter
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    from trak_b200.score_computers import shard_rows
+
+    model = _cifar_resnet18(dev)
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    D = sum(p.numel() for p in params.values())
+    N = 2048
+    lo, hi = shard_rows(total, rank, world)
+    n = hi - lo
+    gen = torch.Generator().manual_seed(rank)
+    host_x = torch.rand(n, 3, 32, 32, generator=gen).pin_memory()
+    host_y = torch.randint(0, 10, (n,), generator=gen).pin_memory()
+
+    def margin(p, x, y):
+        logits = functional_call(model, (p, buffers), (x.unsqueeze(0),))[0]
+        own = torch.arange(logits.numel(), device=logits.device) == y
+        rest = torch.logsumexp(torch.where(own, torch.full_like(logits, -torch.inf), logits), 0)
+        return (logits * own).sum() - rest
+
+    per_sample = vmap(grad(margin), in_dims=(None, 0, 0))
+
+    def out_to_loss(x, y):
+        with torch.no_grad():
+            ps = torch.softmax(model(x), dim=-1)[torch.arange(x.shape[0], device=x.device), y]
+        return (1.0 - ps).unsqueeze(-1)
+
+    tmp = tempfile.mkdtemp(prefix="trak_b200_featurize_")
+    try:
+        gs = mmap_io.create_store(os.path.join(tmp, "grads.mmap"), (n, N), torch.float16)
+        ws = mmap_io.create_store(os.path.join(tmp, "out_to_loss.mmap"), (n, 1), torch.float16)
+        proj = CudaProjector(D, N, 0, ProjectionType.rademacher, dev, 32)
+        fw = FeatureWriter(proj, D ** 0.5, torch.float16, dev, max_batch=batch, grads_store=gs, out_to_loss_store=ws)
+
+        def step(i):
+            x = host_x[i:i + batch].to(dev, non_blocking=True)
+            y = host_y[i:i + batch].to(dev, non_blocking=True)
+            grads = per_sample(params, x, y)
+            return fw.add(grads, np.arange(i, i + x.shape[0]), model_id=0, loss_grads=out_to_loss(x, y))
+
+        step(0)  # warm-up (the rows are written again below)
+        fw.flush()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        last = None
+        for i in range(0, n, batch):
+            last = step(i)
+        fw.flush()
+        torch.cuda.synchronize()
+        sec = torch.tensor([time.perf_counter() - t0], device=dev)
+        if world > 1:
+            dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+        # the last batch as stored against its device-side result (fp16 rounding only)
+        i_last = (n - 1) // batch * batch
+        stored = torch.from_numpy(np.array(gs[i_last:n])).float()
+        diff = float((stored - last.float().cpu()).abs().max() / last.float().abs().max())
+        nz = float((np.array(ws[:64]).astype(np.float32) > 0).mean())
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    fast_jl.free_workspaces()
+    del model, params, proj, fw
+    torch.cuda.empty_cache()
+    return {"metric": "featurize_job_seconds", "value": sec.item(), "unit": "s", "examples_per_s": total / sec.item(),
+            "config": {"workload": f"C3 featurize job: {total} synthetic 3x32x32 images over {world} GPU(s) ({n} on rank 0), "
+                                   f"CIFAR ResNet-18 ({D} parameters, fp32), batch {batch}, vmap(grad) margins -> "
+                                   f"Rademacher k={N} with 1/sqrt(D), margin out-to-loss weights, fp16 grads.mmap / "
+                                   "out_to_loss.mmap per rank"},
+            "stored_vs_device_last_batch": diff, "out_to_loss_rows_positive": nz}
+
+
+def run_chunked(dev):
+    """GPT-2-small (random init, bf16) per-sequence gradients of the mean next-token log-probability for 16
+    sequences of 512 uniform-random tokens (torch.func), projected to k = 8192 by ChunkedCudaProjector straight
+    from the gradient dict: four parameter groups of at most 40M features (the smallest round cap that admits
+    the 38.6M-feature embedding), each with its own seed, summed in the kernel's epilogue."""
+    import torch
+    try:
+        import transformers
+    except Exception as e:
+        return {"unavailable": f"transformers not importable: {e}"}
+    from torch.func import functional_call, grad, vmap
+    from trak_b200 import fast_jl
+    from trak_b200.projectors import make_chunked_projector
+    torch.manual_seed(0)
+    model = transformers.GPT2LMHeadModel(transformers.GPT2Config(attn_implementation="eager")).to(dev, torch.bfloat16).eval()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    widths = [p.numel() for p in params.values()]
+    D, B, S, N = sum(widths), 16, 512, 8192
+    ids = torch.randint(0, 50257, (B, S), generator=torch.Generator().manual_seed(0)).to(dev)
+
+    def mean_next_token_logprob(p, seq):
+        logits = functional_call(model, (p, buffers), (seq.unsqueeze(0),)).logits[0]
+        logp = torch.log_softmax(logits[:-1].float(), dim=-1)
+        return logp.gather(1, seq[1:, None]).mean()
+
+    per_sample = vmap(grad(mean_next_token_logprob), in_dims=(None, 0), chunk_size=4)
+    chunked = make_chunked_projector(widths, N, 0, B, dev, torch.bfloat16, max_chunk_size=40_000_000)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    g_ms = p_ms = 0.0
+    steps = 3
+    for it in range(steps + 1):   # the first pass warms up
+        ev[0].record()
+        grads = per_sample(params, ids)
+        ev[1].record()
+        out = chunked.project(grads, model_id=0)
+        ev[2].record()
+        torch.cuda.synchronize()
+        if it > 0:
+            g_ms += ev[0].elapsed_time(ev[1])
+            p_ms += ev[1].elapsed_time(ev[2])
+        del grads
+    g_ms, p_ms = g_ms / steps, p_ms / steps
+    finite = bool(torch.isfinite(out.float()).all())
+    fast_jl.free_workspaces()
+    del model, params, chunked
+    torch.cuda.empty_cache()
+    peak, _ = measured_peaks()
+    return {"metric": "chunked_projection_examples_per_s", "value": B / (p_ms * 1e-3), "unit": "examples/s",
+            "config": {"workload": f"C5: GPT-2-small ({D} parameters in {len(widths)} tensors, bf16), {B} x {S} tokens, "
+                                   f"vmap(grad) -> ChunkedCudaProjector, 4 parameter groups <= 40M features, Rademacher k={N}"},
+            "projection_ms": p_ms, "gradients_ms": g_ms, "step_examples_per_s": B / ((p_ms + g_ms) * 1e-3),
+            "gradient_gb_per_s": B * D * 2 / (p_ms * 1e-3) / 1e9,
+            "algorithmic_tflops": 2.0 * B * D * N / (p_ms * 1e-3) / 1e12,
+            "frac_of_sustained_peak": 2.0 * B * D * N / (p_ms * 1e-3) / 1e12 / peak, "finite": finite}
 
 
 def run_ours(args, D):
@@ -573,14 +909,51 @@ def run_ours(args, D):
     e2e_value = world * ROWS / e2e_t.item()
     assert torch.equal(host_out, out.cpu()), "end-to-end result differs from the resident-input result"
     g_stage = bufs[1]
-    del host_in, g_stage, g
+    del host_in, g_stage, bufs
+    torch.cuda.empty_cache()
+    extras = not args.no_scoring and not args.no_extras
+    # the other matrix type on the same batch, and the batch split over the ranks
+    other = None
+    if extras:
+        oname, otype = ("rademacher", _lib.TB_RADEMACHER) if ptype == _lib.TB_NORMAL else ("normal", _lib.TB_NORMAL)
+        barrier()
+        o_ms, o_kernel = time_projection(lib, fast_jl, g, otype, calls=max(3, min(args.steps, 10)), warm=2)
+        om = torch.tensor([o_ms, o_kernel], device=dev)
+        if world > 1:
+            dist.all_reduce(om, op=dist.ReduceOp.MAX)
+        o_ms, o_kernel = om.tolist()
+        other = (oname, o_ms, o_kernel)
+    strong = run_scaling_strong(lib, fast_jl, _lib, g, rank, world) if (extras and world > 1) else None
+    _lib.device_status(local)
+    del g
     fast_jl.free_workspaces()
     torch.cuda.empty_cache()
+    sweep = None
+    if extras and rank == 0:
+        try:
+            sweep = run_rows_sweep(lib, fast_jl, _lib, dev, D)
+        except Exception as e:  # an extra measurement must not take the main line down
+            sweep = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    if world > 1:
+        dist.barrier()
     scoring = None if args.no_scoring else run_scoring(args, dev, rank, world, args.scale)
-    try:
-        featurize = None if (args.no_scoring or args.no_featurize) else run_featurize(dev, rank, world)
-    except Exception as e:  # an extra measurement must not take the main line down
-        featurize = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+    def guarded(fn, *a):  # an extra measurement must not take the main line down
+        try:
+            return fn(*a)
+        except Exception as e:
+            return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+    if scoring is not None and extras and args.scale == 1.0:
+        scoring["e2e"] = guarded(run_scoring_e2e, dev, rank, world)
+    do_feat = not (args.no_scoring or args.no_featurize)
+    featurize = guarded(run_featurize, dev, rank, world) if do_feat else None
+    featurize_job = guarded(run_featurize_job, dev, rank, world) if (do_feat and extras) else None
+    chunked = None
+    if do_feat and extras:
+        chunked = guarded(run_chunked, dev) if rank == 0 else None
+        if world > 1:
+            dist.barrier()
 
     if rank == 0:
         peak, peak_note = measured_peaks()
@@ -592,7 +965,10 @@ def run_ours(args, D):
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(D, args.proj_type),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_FULL * D / D_FULL,
+                         "frac": achieved / peak, "frac_burst": achieved / burst_peak(), "peak_burst": burst_peak(),
+                         "traffic": NCU_TRAFFIC_BYTES_FULL["project_kernel"] * D / D_FULL,
+                         "traffic_of_the_whole_call": {k: v * D / D_FULL for k, v in NCU_TRAFFIC_BYTES_FULL.items()},
+                         "algorithmic_bytes_per_launch": ROWS * D * 2 + ROWS * K_DIM * 4,
                          "kernel": f"project_kernel<{args.proj_type}>", "kernel_ms": kernel_ms,
                          "algorithmic_flop_per_launch": flop, "peak_source": peak_note,
                          "note": ("generator-issue-bound: the Gaussian matrix costs ~530 instructions per "
@@ -603,12 +979,31 @@ def run_ours(args, D):
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
         }
+        if other is not None:
+            oname, o_ms, o_kernel = other
+            o_ach = flop / (o_kernel * 1e-3) / 1e12
+            line[oname] = {"value": world * ROWS / (o_ms * 1e-3), "unit": "examples/s", "ms_per_step": o_ms,
+                           "kernel_ms": o_kernel,
+                           "roofline": {"bound": "tensor", "achieved": o_ach, "peak": peak, "unit": "TFLOP/s",
+                                        "frac": o_ach / peak, "frac_burst": o_ach / burst_peak()},
+                           "what": f"the same batch and shape with the {oname} matrix (resident input, CUDA events, "
+                                   "max over ranks)"}
+        if sweep is not None:
+            line["rows_sweep"] = sweep
+        if strong is not None:
+            line["scaling_strong"] = strong
+        line["strict"] = ("timed with strict=False (no device synchronisation after each call); the drop-in default "
+                          "TRAK_B200_STRICT=1 adds a cudaDeviceSynchronize and a status read per call")
         if featurize is not None:
             line["featurize"] = featurize
+        if featurize_job is not None:
+            line["featurize_job"] = featurize_job
+        if chunked is not None:
+            line["chunked"] = chunked
         if scoring is not None:
             line["scoring"] = scoring
             if world == 1 and not args.no_cpu_baseline:
-                scoring["cpu_baseline"] = scoring_cpu_baseline(os.cpu_count() or 1)
+                scoring["cpu_baseline"], scoring["parity"] = scoring_cpu_baseline(os.cpu_count() or 1, dev)
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             sec, measured = cpu_port_sample(ROWS, D, threads, 2)
@@ -635,6 +1030,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-featurize", action="store_true",
                     help="skip the featurize-step measurement (thousands of small PyTorch launches: slow under a profiler)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the secondary measurements (other matrix type, row sweep, strong scaling, scoring end to "
+                         "end, featurize job, chunked projection)")
     ap.add_argument("--no-scoring", action="store_true",
                     help="skip the after-kernel scoring and the featurize-step measurements")
     args = ap.parse_args()

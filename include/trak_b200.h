@@ -142,7 +142,9 @@ int tb_project_segments(int device, void *stream, const tb_segment *segs, int32_
  *                so it is its own transpose) and get_scores' `features @ target_grads.T`
  *                (:187-189, trak/utils.py:128-133).  row_scale (device pointer,
  *                nullable, length M) fuses the out-to-loss weighting that the
- *                reference applies on the host afterwards (trak/traker.py:676-678).
+ *                reference applies on the host afterwards (trak/traker.py:676-678);
+ *                that is the reference's result for ONE checkpoint only -- for several,
+ *                see tb_finalize_scores.
  */
 size_t tb_gram_workspace_bytes(int dtype, int64_t n, int64_t k);
 int tb_gram(int device, void *stream, const void *X, int dtype, int64_t n, int64_t k, int64_t ld,
@@ -157,6 +159,23 @@ int tb_gemm_nt(int device, void *stream, const void *A, int64_t lda, const void 
                int dtype, int64_t M, int64_t N, int64_t K, float *C, int64_t ldc,
                const float *row_scale, float alpha, int accumulate, void *ws, size_t ws_bytes);
 
+/* ---- finalize_scores epilogue ------------------------------------------------------
+ * out[r, c] = (score_sum[r, c] / num_models) * (out_to_loss_sum[r] / num_models)
+ *
+ * The last step of TRAKer.finalize_scores (trak/traker.py:676-678), which the reference
+ * runs with numpy on the host over the whole [n_train, n_targets] array: score_sum is the
+ * sum over the checkpoints of features_m @ target_grads_m^T (accumulate them on the device
+ * with tb_gemm_nt(..., accumulate = 1)), out_to_loss_sum [n] the sum of the checkpoints'
+ * out-to-loss weights (trak/traker.py:667-670), num_models the number of checkpoints used.
+ * `out` is fp32 (TB_F32) or fp16 (TB_F16), the dtype of the scores store
+ * (trak/savers.py:434-451).  Note the difference from tb_gemm_nt's row_scale: that one
+ * weights each checkpoint's product by that checkpoint's own weights (a sum of products),
+ * which equals the reference's product of sums only for ONE checkpoint; with several
+ * checkpoints accumulate unweighted and finish with this call. */
+int tb_finalize_scores(int device, void *stream, const float *score_sum, int64_t ld_sum,
+                       const float *out_to_loss_sum, int64_t n, int64_t m, float num_models,
+                       void *out, int out_dtype, int64_t ld_out);
+
 /* ---- projection without a caller-provided workspace ------------------------------
  * No counterpart in the reference.  Same arguments and result as tb_project, minus
  * `ws` / `ws_bytes`: the scratch lives in a fixed array inside the loaded library
@@ -168,8 +187,13 @@ int tb_gemm_nt(int device, void *stream, const void *A, int64_t lda, const void 
  *
  *   - shapes with tb_project_workspace_bytes(...) > TB_PROJECT_STATIC_SCRATCH_BYTES
  *     are refused with TB_ERR_SCRATCH_LIMIT
+ *   - arguments are checked first, with tb_project's codes; a device that is not a
+ *     B200-class GPU gives TB_ERR_UNSUPPORTED
  *   - the first call on a device looks up the array's device address (a one-time
- *     set-up per device); make that first call before starting any stream capture
+ *     set-up per device); make that first call before starting any stream capture.
+ *     Where the CUDA runtime loads modules lazily, that look-up can be the moment the
+ *     driver sets the array's bytes aside on that GPU: it can then fail for lack of
+ *     device memory (TB_ERR_CUDA, see tb_last_cuda_error); a later call tries again
  *   - all calls on a device share the one array: calls whose kernels may overlap on
  *     the GPU (different streams, different threads) race on it and must be
  *     serialised by the caller.  The array keeps the previous call's bytes; every

@@ -17,6 +17,10 @@ produce the committed golden vectors.
 package, installed by pip into the git-ignored ``baseline/_ref``, which lets one
 GPU test run the unmodified ``TRAKer`` on top of this library.
 
+The reference checkout is found through ``--reference``, the environment variable
+``TRAK_REFERENCE_DIR`` or, failing both, a directory named ``reference`` next to this
+repository.
+
 Usage:  python oracle/build_ref.py [--reference /path/to/reference]
 """
 import argparse
@@ -30,10 +34,19 @@ OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "fast_jl.so")
 
 
-def build(reference: str = "/root/reference", force: bool = False) -> str | None:
+def default_reference() -> str:
+    """Where the reference checkout is expected when no path is given."""
+    env = os.environ.get("TRAK_REFERENCE_DIR")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference: str = None, force: bool = False) -> str | None:
     """Compile the reference extension; returns the path or None if the
     reference checkout is absent (e.g. on a machine that only has the
     prebuilt file)."""
+    reference = reference or default_reference()
     src = os.path.join(reference, "fast_jl", "fast_jl.cu")
     if not os.path.exists(src):
         return OUT if os.path.exists(OUT) else None
@@ -66,11 +79,12 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
 PY_DIR = os.path.join(os.path.dirname(HERE), "baseline", "_ref")
 
 
-def install_python_package(reference: str = "/root/reference", force: bool = False) -> str | None:
+def install_python_package(reference: str = None, force: bool = False) -> str | None:
     """Install the reference's pure-Python package (``trak``) with pip, offline and without
     dependencies, into the git-ignored ``baseline/_ref`` directory, so that a GPU test can drive
     this library through the unmodified ``TRAKer``.  Returns the directory, or None when neither
     the checkout nor an earlier install is there."""
+    reference = reference or default_reference()
     done = os.path.isdir(os.path.join(PY_DIR, "trak"))
     if not os.path.exists(os.path.join(reference, "setup.py")) or (done and not force):
         return PY_DIR if done else None
@@ -95,7 +109,7 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference())
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     p = build(a.reference, a.force)

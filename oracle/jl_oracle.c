@@ -183,60 +183,83 @@ int tbo_matrix_rows(int ptype, uint64_t F, uint32_t N, uint32_t seed, uint32_t t
 /* dtype: 0 fp16, 1 bf16, 2 fp32, 3 fp64.  round_f16 != 0 rounds each input to
  * fp16 first, as the reference does for fp32 inputs (data_loading.cuh:10).
  * out[b*N + n] = sum_f G[b*ld + f] * P[f, n]. */
+static void project_column_group(int ptype, const void *G, int dtype, uint64_t B, uint64_t F, uint64_t ld,
+                                 const geom *g, uint32_t seed, int round_f16, uint32_t w, double *out,
+                                 uint64_t out_ld, uint64_t out_col0) {
+    /* the 32 output columns 32w .. 32w+31, written to out[b*out_ld + out_col0 + nl] */
+    uint32_t ntiles_used = (uint32_t)((F - 1) / g->fts + 1);
+    double *acc = (double *)calloc((size_t)B * 32, sizeof(double));
+    float *gin = (float *)malloc(sizeof(float) * B * 16);
+    float tile[16 * 32];
+    xw_state st[32];
+    for (uint32_t by = 0; by < ntiles_used; by++) {
+        uint64_t f0 = (uint64_t)by * g->fts;
+        uint64_t len = F - f0 < g->fts ? F - f0 : g->fts;
+        for (int L = 0; L < 32; L++) xw_seed(&st[L], stream_seed(seed, w * 32 + L, by));
+        for (uint64_t t0 = 0; t0 < len; t0 += 16) {
+            factor_tile(ptype, st, tile);
+            int kk = (int)(len - t0 < 16 ? len - t0 : 16);
+            for (uint64_t b = 0; b < B; b++)
+                for (int k = 0; k < kk; k++) {
+                    size_t idx = (size_t)b * ld + f0 + t0 + k;
+                    float x;
+                    switch (dtype) {
+                    case 0: x = (float)((const _Float16 *)G)[idx]; break;
+                    case 1: x = bf16_to_f32(((const uint16_t *)G)[idx]); break;
+                    case 2: x = ((const float *)G)[idx]; break;
+                    default: x = 0; break;
+                    }
+                    if (dtype == 3) {
+                        double xd = ((const double *)G)[idx];
+                        gin[b * 16 + k] = 0;
+                        /* fp64 inputs bypass the float staging below */
+                        for (int nl = 0; nl < 32; nl++) acc[b * 32 + nl] += xd * (double)tile[k * 32 + nl];
+                        continue;
+                    }
+                    if (round_f16) x = f16_round(x);
+                    gin[b * 16 + k] = x;
+                }
+            if (dtype != 3)
+                for (uint64_t b = 0; b < B; b++)
+                    for (int k = 0; k < kk; k++) {
+                        double x = (double)gin[b * 16 + k];
+                        const float *row = tile + k * 32;
+                        double *a = acc + b * 32;
+                        for (int nl = 0; nl < 32; nl++) a[nl] += x * (double)row[nl];
+                    }
+        }
+    }
+    for (uint64_t b = 0; b < B; b++)
+        for (int nl = 0; nl < 32; nl++) out[b * out_ld + out_col0 + nl] = acc[b * 32 + nl];
+    free(acc);
+    free(gin);
+}
+
 int tbo_project(int ptype, const void *G, int dtype, uint64_t B, uint64_t F, uint64_t ld,
                 uint32_t N, uint32_t seed, uint32_t tiles, int round_f16, double *out) {
     geom g;
     if (make_geom(&g, F, N, tiles)) return -1;
     if (dtype < 0 || dtype > 3) return -3;
     memset(out, 0, sizeof(double) * B * N);
-    uint32_t ntiles_used = (uint32_t)((F - 1) / g.fts + 1);
 #pragma omp parallel for schedule(dynamic, 1)
-    for (uint32_t w = 0; w < N / 32; w++) {
-        double *acc = (double *)calloc((size_t)B * 32, sizeof(double));
-        float *gin = (float *)malloc(sizeof(float) * B * 16);
-        float tile[16 * 32];
-        xw_state st[32];
-        for (uint32_t by = 0; by < ntiles_used; by++) {
-            uint64_t f0 = (uint64_t)by * g.fts;
-            uint64_t len = F - f0 < g.fts ? F - f0 : g.fts;
-            for (int L = 0; L < 32; L++) xw_seed(&st[L], stream_seed(seed, w * 32 + L, by));
-            for (uint64_t t0 = 0; t0 < len; t0 += 16) {
-                factor_tile(ptype, st, tile);
-                int kk = (int)(len - t0 < 16 ? len - t0 : 16);
-                for (uint64_t b = 0; b < B; b++)
-                    for (int k = 0; k < kk; k++) {
-                        size_t idx = (size_t)b * ld + f0 + t0 + k;
-                        float x;
-                        switch (dtype) {
-                        case 0: x = (float)((const _Float16 *)G)[idx]; break;
-                        case 1: x = bf16_to_f32(((const uint16_t *)G)[idx]); break;
-                        case 2: x = ((const float *)G)[idx]; break;
-                        default: x = 0; break;
-                        }
-                        if (dtype == 3) {
-                            double xd = ((const double *)G)[idx];
-                            gin[b * 16 + k] = 0;
-                            /* fp64 inputs bypass the float staging below */
-                            for (int nl = 0; nl < 32; nl++) acc[b * 32 + nl] += xd * (double)tile[k * 32 + nl];
-                            continue;
-                        }
-                        if (round_f16) x = f16_round(x);
-                        gin[b * 16 + k] = x;
-                    }
-                if (dtype != 3)
-                    for (uint64_t b = 0; b < B; b++)
-                        for (int k = 0; k < kk; k++) {
-                            double x = (double)gin[b * 16 + k];
-                            const float *row = tile + k * 32;
-                            double *a = acc + b * 32;
-                            for (int nl = 0; nl < 32; nl++) a[nl] += x * (double)row[nl];
-                        }
-            }
-        }
-        for (uint64_t b = 0; b < B; b++)
-            for (int nl = 0; nl < 32; nl++) out[b * N + w * 32 + nl] = acc[b * 32 + nl];
-        free(acc);
-        free(gin);
-    }
+    for (uint32_t w = 0; w < N / 32; w++)
+        project_column_group(ptype, G, dtype, B, F, ld, &g, seed, round_f16, w, out, N, (uint64_t)w * 32);
+    return 0;
+}
+
+/* The same for some 32-column groups only (a column of the matrix does not depend on how many columns
+ * there are): out[b*(32*ngroups) + 32*i + nl] = sum_f G[b*ld + f] * P[f, 32*groups[i] + nl].  Lets a test
+ * check a few columns of a projection whose full oracle would take minutes. */
+int tbo_project_column_groups(int ptype, const void *G, int dtype, uint64_t B, uint64_t F, uint64_t ld,
+                              uint32_t seed, uint32_t tiles, int round_f16, const uint32_t *groups,
+                              uint32_t ngroups, double *out) {
+    geom g;
+    if (ngroups == 0 || make_geom(&g, F, 32, tiles)) return -1;
+    if (dtype < 0 || dtype > 3) return -3;
+    memset(out, 0, sizeof(double) * B * 32 * ngroups);
+#pragma omp parallel for schedule(dynamic, 1)
+    for (uint32_t i = 0; i < ngroups; i++)
+        project_column_group(ptype, G, dtype, B, F, ld, &g, seed, round_f16, groups[i], out,
+                             (uint64_t)32 * ngroups, (uint64_t)i * 32);
     return 0;
 }

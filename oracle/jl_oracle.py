@@ -52,6 +52,8 @@ def lib():
         l.tbo_matrix_rows.restype = i
         l.tbo_project.argtypes = [i, vp, i, u64, u64, u64, u32, u32, u32, i, vp]
         l.tbo_project.restype = i
+        l.tbo_project_column_groups.argtypes = [i, vp, i, u64, u64, u64, u32, u32, i, vp, u32, vp]
+        l.tbo_project_column_groups.restype = i
         _lib = l
     return _lib
 
@@ -109,6 +111,22 @@ def project(ptype, grads, N: int, seed: int, tiles: int, round_f16: bool = False
                            int(round_f16), out.ctypes.data)
     if rc:
         raise ValueError(f"tbo_project failed: {rc}")
+    return out
+
+
+def project_column_groups(ptype, grads, seed: int, tiles: int, groups, round_f16: bool = False) -> np.ndarray:
+    """The columns ``32 g .. 32 g + 31`` for every ``g`` in ``groups`` of the fp64-accumulated projection
+    (``[B, 32 * len(groups)]``, groups side by side): a few columns of a projection whose full oracle would
+    take minutes.  Columns do not depend on the projection dimension."""
+    g = np.ascontiguousarray(grads)
+    dt = 1 if g.dtype == np.uint16 else _DT[g.dtype]
+    groups = np.ascontiguousarray(np.asarray(groups, dtype=np.uint32))
+    B, F = g.shape
+    out = np.empty((B, 32 * len(groups)), np.float64)
+    rc = lib().tbo_project_column_groups(_ptype(ptype), g.ctypes.data, dt, B, F, F, seed, tiles, int(round_f16),
+                                         groups.ctypes.data, len(groups), out.ctypes.data)
+    if rc:
+        raise ValueError(f"tbo_project_column_groups failed: {rc}")
     return out
 
 

@@ -1,7 +1,7 @@
 """Generates ``mmapsaver_*.mmap``: stores written by the UNMODIFIED reference ``MmapSaver``
 (trak/savers.py:241-457) for a tiny checkpoint, filled with known values.
 
-    python tests/golden/make_mmapsaver_golden.py --reference /root/reference
+    python tests/golden/make_mmapsaver_golden.py --reference /path/to/trak
 
 They pin the byte layout that ``trak_b200/mmap_io.py`` has to read and reproduce.
 """
@@ -24,7 +24,7 @@ def values(shape, dtype, offset=0.0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of MadryLab/trak")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from trak.savers import MmapSaver

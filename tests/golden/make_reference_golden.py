@@ -3,7 +3,7 @@
 
 Run where the reference checkout is importable:
 
-    python tests/golden/make_reference_golden.py --reference /root/reference
+    python tests/golden/make_reference_golden.py --reference /path/to/trak
 
 The fixtures pin the CPU restatement in ``oracle/basic_ref.py`` and serve as
 the expected values of the scoring parity tests.  Inputs are regenerated from
@@ -21,7 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of MadryLab/trak")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from trak.projectors import BasicProjector

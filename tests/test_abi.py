@@ -44,10 +44,13 @@ def test_project_workspace_query():
     assert 0 < small < big
     # staged copy (128 rows x 148 tiles x 75520 padded features x 2 B) + partials
     assert big >= 128 * 148 * 75520 * 2
-    # batches are walked at most 256 rows at a time: the workspace stops growing there
+    # batches are walked at most 512 rows at a time: the workspace stops growing there
     big256 = lib.tb_project_workspace_bytes(0, 256, 11173962, 4096, 148)
-    assert big < big256 <= 2 * big
-    assert lib.tb_project_workspace_bytes(0, 1024, 11173962, 4096, 148) == big256
+    big512 = lib.tb_project_workspace_bytes(0, 512, 11173962, 4096, 148)
+    assert big < big256 <= 2 * big and big256 < big512 <= 2 * big256
+    assert lib.tb_project_workspace_bytes(0, 1024, 11173962, 4096, 148) == big512
+    # passes of more than 256 rows are padded to a multiple of 32 rows, smaller ones to 16
+    assert lib.tb_project_workspace_bytes(0, 257, 11173962, 4096, 148) >= 288 * 148 * 75520 * 2
 
 
 def _call(**kw):
@@ -70,6 +73,21 @@ def _call(**kw):
 def test_project_argument_validation(kw, code):
     # all of these are rejected on the host, before any CUDA call
     assert _call(**kw) == code
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dtype=7), 1), (dict(B=0), 2), (dict(ld=999), 2), (dict(N=500), 3), (dict(N=500, F=10 ** 9, ld=10 ** 9), 3),
+    (dict(grads=None), 4), (dict(out=0x2004), 4), (dict(ptype=2), 4),
+    (dict(B=128, F=2_000_000, ld=2_000_000, N=4096, ld_out=4096), 9),
+])
+def test_static_entry_validates_like_tb_project_before_touching_a_device(kw, code):
+    # same codes as tb_project for bad arguments, then the scratch limit; all on the host
+    lib = _lib.lib()
+    a = dict(device=0, stream=None, grads=0x1000, dtype=0, B=8, F=1000, ld=1000, out=0x2000, ld_out=512,
+             N=512, seed=0, tiles=148, ptype=0, alpha=1.0, acc=0)
+    a.update(kw)
+    assert lib.tb_project_static(a["device"], a["stream"], a["grads"], a["dtype"], a["B"], a["F"], a["ld"], a["out"],
+                                 a["ld_out"], a["N"], a["seed"], a["tiles"], a["ptype"], a["alpha"], a["acc"]) == code
 
 
 def test_check_maps_codes_to_reference_exception_types():

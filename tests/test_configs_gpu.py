@@ -155,3 +155,86 @@ def test_cifar_resnet18_per_sample_gradients_to_2048_rademacher(cuda):
     got = feats[rows].cpu().numpy().astype(np.float64)
     rel = np.linalg.norm(got - ref, axis=1) / np.linalg.norm(ref, axis=1)
     assert rel.max() <= 1e-3, rel
+
+
+def test_gpt2_small_real_gradients_through_the_chunked_projector(cuda):
+    """GPT-2-small (random init, bf16, 124,439,808 parameters in 148 tensors), 16 sequences of 512 uniform-random
+    tokens, per-sequence gradients of the mean next-token log-probability from torch.func, projected to 8192 by
+    the chunked projector straight from the gradient dict.  Two real rows are checked against the fp64 oracle on
+    three 32-column groups: the sum over the chunks of each chunk's own projection (own seed)."""
+    transformers = pytest.importorskip("transformers")
+    from torch.func import functional_call, grad, vmap
+    from trak_b200.projectors import make_chunked_projector
+    torch.manual_seed(0)
+    model = transformers.GPT2LMHeadModel(transformers.GPT2Config(attn_implementation="eager")).to(cuda, torch.bfloat16).eval()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    widths = [p.numel() for p in params.values()]
+    assert len(widths) == 148 and sum(widths) == 124_439_808 and max(widths) == 38_597_376
+    B, S, N = 16, 512, 8192
+    ids = torch.randint(0, 50257, (B, S), generator=torch.Generator().manual_seed(0)).to(cuda)
+
+    def mean_next_token_logprob(p, seq):
+        logits = functional_call(model, (p, buffers), (seq.unsqueeze(0),)).logits[0]
+        logp = torch.log_softmax(logits[:-1].float(), dim=-1)
+        return logp.gather(1, seq[1:, None]).mean()
+
+    grads = vmap(grad(mean_next_token_logprob), in_dims=(None, 0), chunk_size=4)(params, ids)
+    assert all(g.dtype == torch.bfloat16 and g.shape[0] == B for g in grads.values())
+    # the reference's cap for this batch (2^32 / 16) admits the whole model in one chunk; 40M features per
+    # chunk (the smallest round cap that admits the 38.6M-feature embedding) gives four
+    chunked = make_chunked_projector(widths, N, 0, B, cuda, torch.float32, max_chunk_size=40_000_000)
+    sizes = chunked.params_per_chunk
+    assert len(sizes) == 4 and min(sizes) > 0 and sum(sizes) == sum(widths)
+    out = chunked.project(grads, model_id=0)
+    assert out.shape == (B, N) and out.dtype == torch.float32 and bool(torch.isfinite(out).all())
+
+    rows, groups = [0, 7], [0, 100, 255]
+    want = np.zeros((len(rows), 32 * len(groups)))
+    vals, at = list(grads.values()), 0
+    for size, proj in zip(sizes, chunked.projector_per_chunk):
+        part, width = [], 0
+        while width < size:
+            part.append(vals[at][rows].reshape(len(rows), -1))
+            width += part[-1].shape[1]
+            at += 1
+        assert width == size
+        flat = torch.cat(part, dim=1).contiguous().view(torch.uint16).cpu().numpy()    # bf16 bit patterns
+        want += o.project_column_groups(o.RADEMACHER, flat, proj.seed, proj.num_sms, groups)
+    cols = np.concatenate([np.arange(32 * g, 32 * g + 32) for g in groups])
+    got = out[rows][:, cols].double().cpu().numpy()
+    rel = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+    print("GPT-2-small real gradients, rows 0 and 7 on 96 columns against the fp64 oracle:", rel)
+    assert rel.max() <= 1e-3, rel
+
+
+def test_feature_writer_fills_the_stores_like_featurize(cuda, tmp_path):
+    """FeatureWriter against the reference's per-batch arithmetic (trak/traker.py:424-437): project, divide by
+    sqrt(num_params), cast to the store dtype, write rows `inds`; out-to-loss weights beside them.  Batches in
+    shuffled index order, a ragged last batch, more batches than staging slots."""
+    from trak_b200 import mmap_io
+    from trak_b200.featurize import FeatureWriter
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    n, D, k, bs = 1000, 5003, 512, 96
+    g = torch.Generator(device=cuda).manual_seed(0)
+    grads = torch.randn(n, D, device=cuda, generator=g)
+    o2l = torch.rand(n, 1, device=cuda, generator=g)
+    proj = CudaProjector(D, k, 3, ProjectionType.rademacher, cuda, 32)
+    perm = np.random.default_rng(0).permutation(n)
+    for dtype in (torch.float16, torch.float32):
+        tag = str(dtype).split(".")[-1]
+        gs = mmap_io.create_store(tmp_path / tag / "grads.mmap", (n, k), dtype)
+        ws = mmap_io.create_store(tmp_path / tag / "out_to_loss.mmap", (n, 1), dtype)
+        fw = FeatureWriter(proj, D ** 0.5, dtype, cuda, max_batch=bs, grads_store=gs, out_to_loss_store=ws, slots=3,
+                           keep_on_device=True)
+        for i in range(0, n, bs):
+            inds = perm[i:i + bs]
+            idx = torch.as_tensor(inds, device=cuda)
+            fw.add(grads[idx], inds, model_id=0, loss_grads=o2l[idx])
+        fw.flush()
+        want = (proj.project(grads, model_id=0) / D ** 0.5).to(dtype).cpu()
+        got = torch.from_numpy(np.array(mmap_io.open_store(tmp_path / tag / "grads.mmap", mode="r")))
+        # alpha is applied inside the kernel before the cast, the reference divides afterwards: one rounding apart
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-3 if dtype == torch.float16 else 1e-6, atol=1e-6)
+        assert torch.equal(torch.from_numpy(np.array(ws)), o2l.to(dtype).cpu())
+        assert torch.equal(fw.features_device.cpu(), got)

@@ -83,3 +83,38 @@ def test_chunked_projector_detects_inconsistent_chunking():
                                          dtype=torch.float32)
     with pytest.raises(AssertionError):
         cp.project(grads, model_id=0)
+
+
+def test_parameter_chunk_sizes_follow_the_reference_rule():
+    # expected values produced by the unmodified trak.utils.get_parameter_chunk_sizes on this model
+    m = torch.nn.Sequential(torch.nn.Linear(300, 200), torch.nn.Linear(200, 100), torch.nn.Linear(100, 7))
+    want = {50000: (85899, [81007]), 70000: (61356, [60200, 20807]), 200000: (21474, [0, 60000, 21007]),
+            2 ** 20: (4095, [0, 60000, 200, 20000, 807])}
+    for bs, (cap, sizes) in want.items():
+        assert projectors.get_parameter_chunk_sizes(m, bs) == (cap, sizes)
+    widths = [p.numel() for p in m.parameters()]
+    assert projectors.get_parameter_chunk_sizes(widths, max_chunk_size=61356)[1] == [60200, 20807]
+    with pytest.raises(ValueError):
+        projectors.get_parameter_chunk_sizes(widths)
+
+
+def test_chunked_projector_rejects_empty_chunks_and_oversized_batches():
+    grads = {"a": torch.ones(2, 9), "b": torch.ones(2, 3)}
+    cp = projectors.ChunkedCudaProjector([_FakeProjector(1), _FakeProjector(1), _FakeProjector(1)], max_chunk_size=8,
+                                         params_per_chunk=[0, 9, 3], feat_bs=2, device=torch.device("cpu"),
+                                         dtype=torch.float32)
+    with pytest.raises(ValueError, match="larger than"):
+        cp.project(grads, model_id=0)       # the first parameter alone exceeds the cap: empty leading chunk
+    cp2 = projectors.ChunkedCudaProjector([_FakeProjector(1)], max_chunk_size=100, params_per_chunk=[12], feat_bs=1,
+                                          device=torch.device("cpu"), dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="feat_bs"):
+        cp2.project(grads, model_id=0)      # two rows into a projector sized for one
+
+
+def test_finalize_and_featurize_components_need_a_cuda_device():
+    from trak_b200.featurize import FeatureWriter
+    from trak_b200.finalize import ScoreFinalizer
+    with pytest.raises(ValueError):
+        ScoreFinalizer([torch.zeros(4, 2)], [torch.zeros(3, 2)], [torch.zeros(4, 1)], "cpu")
+    with pytest.raises(ValueError):
+        FeatureWriter(_FakeProjector(1), 1.0, torch.float32, "cpu", max_batch=4)

@@ -48,3 +48,18 @@ def test_projection_of_random_inputs(gold, case):
             want = gold[f"proj_{case}_{dn}_{name}"].astype(np.float64)
             err = (np.linalg.norm(ref - want, axis=1) / np.linalg.norm(want, axis=1)).max()
             assert err < 2e-5, (dn, name, err)
+
+
+def test_column_group_subset_equals_the_full_oracle_projection():
+    """project_column_groups (used where the full oracle would take minutes) gives exactly the columns of the
+    full projection, for both matrix types and whatever the projection dimension."""
+    import numpy as np
+    from oracle import jl_oracle as o
+    g = np.random.default_rng(0).standard_normal((3, 5000)).astype(np.float16)
+    for p in (o.RADEMACHER, o.NORMAL):
+        full = o.project(p, g, 512, 7, 37)
+        part = o.project_column_groups(p, g, 7, 37, [0, 5, 15])
+        assert np.array_equal(part[:, :32], full[:, :32])
+        assert np.array_equal(part[:, 32:64], full[:, 160:192])
+        assert np.array_equal(part[:, 64:], full[:, 480:512])
+        assert np.array_equal(o.project(p, g, 1024, 7, 37)[:, 160:192], part[:, 32:64])

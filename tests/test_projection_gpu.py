@@ -72,7 +72,7 @@ def test_parity_with_oracle(cuda, p, dt, B, F, N, seed, T):
         ref = o.project(p, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
     assert rel_rows(out, ref) <= TOL
     if dt == "f32":
-        # still within tolerance of the un-rounded fp32 input (how north-star states it)
+        # still within tolerance of the fp64 product of the un-rounded fp32 gradients
         assert rel_rows(out, o.project(p, g_cpu.numpy(), N, seed, T)) <= TOL
 
 
@@ -325,6 +325,78 @@ def test_bit_exact_matrix_and_parity_vs_reference_kernel(cuda, B, F, N, seed, T)
             ref_fn = getattr(w, f"project_{name}_32")
             assert torch.equal(ours(g1, N, seed, T, p), ref_fn(g1, N, seed, T))
             assert rel_rows(ours(g, N, seed, T, p).cpu().numpy(), ref_fn(g, N, seed, T).cpu().numpy()) <= TOL
+
+
+def test_full_benchmark_shape_all_rows_against_the_reference_kernel(cuda):
+    """The benchmark's own launch (fp16 [128 x 11,173,962] -> 4096, seed 17, 148 tiles), every row, both
+    matrix types, against the reference's compiled kernel on the same input: one-hot rows (matrix entries at
+    the ends of the feature range and of a tile) bit for bit, the 120 random rows within tolerance."""
+    w = _witness()
+    B, F, N, seed, T = 128, 11_173_962, 4096, 17, 148
+    fts = o.feature_tile_size(F, T)
+    feats = [0, 1, 15, 16, fts - 1, fts, 73 * fts + 40_001, F - 1]
+    g = (torch.randn(B, F, device=cuda, generator=torch.Generator(device=cuda).manual_seed(1000)) * 1e-2).half()
+    for i, f in enumerate(feats):
+        g[i].zero_()
+        g[i, f] = 1.0
+    for name, p in (("rademacher", RAD), ("normal", NOR)):
+        got = ours(g, N, seed, T, p)
+        ref = getattr(w, f"project_{name}_32")(g, N, seed, T)
+        assert torch.equal(got[:len(feats)], ref[:len(feats)]), name
+        err = ((got - ref).double().norm(dim=1) / ref.double().norm(dim=1))[len(feats):].max().item()
+        print(f"{name}: 120 random rows against the reference kernel, worst row {err:.2e}")
+        assert err <= TOL, (name, err)
+        del got, ref
+
+
+WIDE_SHAPES = [  # B, F, N, seed, tiles, dtype: batches that take the 512-row Gaussian kernel
+    (512, 20011, 1024, 17, 148, "f16"),
+    (300, 75_531, 512, 5, 37, "bf16"),
+    (257, 9473, 512, 99, 7, "f32"),     # fewer tiles than generator groups
+    (600, 3001, 512, 3, 148, "f16"),    # 512 rows, then 88 through the narrow kernel
+    (384, 4096, 1536, 4, 4, "f16"),     # tile size a multiple of 64
+    (290, 130, 512, 8, 148, "f32"),     # fewer features than tiles
+]
+
+
+@pytest.mark.parametrize("B,F,N,seed,T,dt", WIDE_SHAPES)
+def test_wide_gaussian_batches(cuda, B, F, N, seed, T, dt):
+    """More than 256 rows of a Gaussian projection go through one generation of the matrix (operand staged
+    in shared memory).  One-hot rows must give the very bits the narrow kernel gives (which the tests above
+    tie to the reference kernel); random rows are checked against the fp64 oracle."""
+    g_cpu = (torch.randn(B, F, generator=torch.Generator().manual_seed(B + F)) * 1e-1).to(DT[dt])
+    fts = o.feature_tile_size(F, T)
+    feats = sorted({0, 1, min(F - 1, 15), min(F - 1, 16), min(F - 1, fts - 1), min(F - 1, fts), F // 2, F - 1})
+    hot_rows = [0, 1, 2, 100, 255, 256, B - 2, B - 1][:len(feats)]   # spread over both halves of the batch
+    for r, f in zip(hot_rows, feats):
+        g_cpu[r].zero_()
+        g_cpu[r, f] = 1.0
+    g = g_cpu.to(cuda)
+    wide = ours(g, N, seed, T, NOR)
+    narrow = torch.cat([ours(g[i:i + 200].contiguous(), N, seed, T, NOR) for i in range(0, B, 200)])
+    assert torch.equal(wide[hot_rows], narrow[hot_rows])
+    assert rel_rows(wide.cpu().numpy(), narrow.cpu().numpy()) <= 1e-5
+    assert torch.equal(wide, ours(g, N, seed, T, NOR))            # run-to-run identical
+    if B * F * N <= 6e12:
+        ref = o.project(NOR, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
+        keep = [r for r in range(B) if r not in hot_rows]
+        # for bf16 gradients the kernel rounds the fp16-valued matrix once more to bf16 (about 2^-9 per entry,
+        # unbiased): the rows are still within tolerance of the oracle's fp16-valued matrix
+        assert rel_rows(wide.cpu().numpy()[keep], ref[keep]) <= (TOL if dt != "bf16" else 4e-3)
+    # alpha and accumulation through the wide path
+    out = torch.full((B, N), 0.5, device=cuda)
+    ours(g, N, seed, T, NOR, alpha=0.25, out=out, accumulate=True)
+    torch.testing.assert_close(out, 0.5 + 0.25 * wide, rtol=1e-6, atol=1e-5)
+
+
+def test_wide_gaussian_from_segments(cuda):
+    from trak_b200 import fast_jl
+    B = 320
+    shapes = [(64, 3, 3, 3), (), (17,), (129, 31), (300, 7, 2)]
+    tensors = [torch.randn((B,) + sh, device=cuda) for sh in shapes]
+    flat = torch.cat([t.reshape(B, 1) if t.dim() < 2 else t.flatten(start_dim=1) for t in tensors], dim=1)
+    a = fast_jl.project_segments(tensors, 1024, 21, 148, NOR)
+    assert torch.equal(a, fast_jl.project(flat.contiguous(), 1024, 21, 148, NOR))
 
 
 def test_bounded_wait_times_out_and_device_stays_usable(cuda):

@@ -2,8 +2,8 @@
 BasicScoreComputer: against fixtures produced by the unmodified reference and against
 its CPU port on seeded inputs.
 
-Tolerance: Frobenius-relative 1e-3 for Gram, features and scores (what north-star
-states for the scores); the fp32 bf16-split GEMMs land around 1e-5.
+Tolerance: Frobenius-relative 1e-3 for Gram, features and scores; the three-pass fp16-split
+GEMMs land around 1e-5.
 """
 import os
 
@@ -260,3 +260,55 @@ def test_scores_without_forming_the_features(cuda):
     s_ref = torch.zeros(n, m)
     br.scores(br.x_xtx_inv(X, br.xtx(X), lam), T, s_ref)
     assert rel(direct, br.finalize_scores_epilogue(s_ref, w, 1)) <= TOL
+
+
+def test_pipeline_at_the_benchmark_projection_dim(cuda):
+    """k = 8192, the size the scoring benchmark runs at (X ~ N(0, 1/k), lambda = 1e-3): Gram, rescaled inverse,
+    features and scores of get_xtx -> get_x_xtx_inv -> get_scores (and of get_scores_from_grads) against the CPU
+    port of BasicScoreComputer on the same inputs, each within 1e-3 Frobenius-relative.  At this size the
+    inverse runs 16 block columns of the two-level Cholesky, the tensor-core merge levels 1024, 2048 and 4096
+    and the 1056-tile symmetric W^T W."""
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m, lam = 16_384, 8192, 512, 1e-3
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    X = torch.randn(n, k, generator=torch.Generator().manual_seed(2000)) / k ** 0.5
+    T = torch.randn(m, k, generator=torch.Generator().manual_seed(3000)) / k ** 0.5
+    w = torch.rand(n, 1, generator=torch.Generator().manual_seed(4000))
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, lambda_reg=lam)
+    gram = sc.get_xtx(X)
+    feats = sc.get_x_xtx_inv(X, gram)
+    acc = torch.zeros(n, m)
+    sc.get_scores(feats, T, acc)
+    direct = torch.zeros(n, m)
+    sc.get_scores_from_grads(X, gram, T, direct, row_scale=w)
+
+    g_ref = br.xtx(X)
+    inv_ref = br.xtx_inverse(g_ref, lam)
+    f_ref = br.x_xtx_inv(X, g_ref, lam)
+    s_ref = torch.zeros(n, m)
+    br.scores(f_ref, T, s_ref)
+    from trak_b200 import score_computers as scm
+    inv = scm.spd_inverse_(gram.to(cuda).float().clone(), lam, rescale=True)
+    errs = {"gram": rel(gram, g_ref), "inverse": rel(inv, inv_ref), "features": rel(feats, f_ref),
+            "scores": rel(acc, s_ref), "scores_from_grads": rel(direct, br.finalize_scores_epilogue(s_ref, w, 1))}
+    print("k = 8192 against the CPU port:", {a: f"{b:.2e}" for a, b in errs.items()})
+    for name, e in errs.items():
+        assert e <= TOL, (name, errs)
+
+
+def test_inverse_at_8192_against_an_fp64_inverse(cuda):
+    from trak_b200 import score_computers as sc
+    k, lam = 8192, 1e-3
+    g = torch.Generator(device=cuda).manual_seed(8192)
+    A = torch.zeros(k, k, device=cuda, dtype=torch.float64)
+    for _ in range(3):   # Gram of 3k rows of N(0, 1/k), formed block-wise in fp64
+        y = torch.randn(k, k, device=cuda, generator=g, dtype=torch.float64) / k ** 0.5
+        A += y.T @ y
+    A32 = A.float()
+    ref = torch.linalg.inv(A32.double() + lam * torch.eye(k, device=cuda, dtype=torch.float64))
+    inv = sc.spd_inverse_(A32.clone(), lam, rescale=False)
+    assert torch.equal(inv, inv.T)
+    err = rel(inv, ref)
+    assert err <= 2e-5, err
+    inv2 = sc.spd_inverse_(A32.clone(), lam, rescale=True)
+    assert rel(inv2, ref / ref.abs().mean()) <= 2e-5

@@ -10,7 +10,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libtrakb200.so")
-SOURCES = ["api.cu", "project.cu", "project_static.cu", "gemm.cu", "inverse.cu"]
+SOURCES = ["api.cu", "project.cu", "project_static.cu", "gemm.cu", "inverse.cu", "finalize.cu"]
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

@@ -64,12 +64,6 @@ struct GemmParams {
                              // diagonal are computed and every result is stored twice
 };
 
-// K-major tile, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) |
-           (4ull << 61);
-}
-
 // Power-of-two scale of a packed fp32 operand row whose largest magnitude has the bit pattern
 // `amax_bits`: the biased exponent E is clamped to [16, 254] so that both 2^(141 - E) (brings
 // the maximum into [2^14, 2^15), inside fp16's range) and its inverse are normal numbers.

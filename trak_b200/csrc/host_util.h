@@ -25,6 +25,10 @@ void set_cuda_error(const char* what, const char* file, int line);
 // TB_OK if `device` exists and is compute capability 10.x; sets it current.
 int select_device(int device, int* sm_count);
 
+// TB_OK, or the code tb_project returns for these arguments before it looks at workspace or device.
+int validate_project_args(const void* grads, int dtype, int64_t B, int64_t F, int64_t ld, const float* out,
+                          int64_t ld_out, uint32_t N, uint32_t num_feature_tiles, int proj_type);
+
 // Device address of the status word of `device` (valid after select_device).
 uint32_t* status_ptr(int device);
 

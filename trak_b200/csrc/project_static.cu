@@ -24,16 +24,19 @@ static std::mutex g_scratch_mu;
 static void* g_scratch_ptr[64];  // device address of g_project_scratch, per device
 
 // In host code the array's name is only a handle for the runtime, not a device address.
-// The address is looked up once per device, with that device current.
+// The address is looked up once per device, with that device current (select_device has made it
+// so).  With the runtime's lazy module loading this look-up can be the moment the driver sets
+// the array's bytes aside on that GPU, so it can fail for lack of memory; a failure is reported,
+// not remembered, and leaves no error pending in the runtime.
 static int scratch_address(int device, void** out) {
-    if (device < 0 || device >= 64) return TB_ERR_BAD_ARG;
     std::lock_guard<std::mutex> lk(g_scratch_mu);
     if (!g_scratch_ptr[device]) {
-        TB_CUDA(cudaSetDevice(device));
         void* p = nullptr;
-        TB_CUDA(cudaGetSymbolAddress(&p, g_project_scratch));
-        if (!p) {
-            set_cuda_error("cudaGetSymbolAddress returned a null address", __FILE__, __LINE__);
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_project_scratch);
+        if (e != cudaSuccess || !p) {
+            set_cuda_error(e != cudaSuccess ? cudaGetErrorString(e) : "cudaGetSymbolAddress returned a null address",
+                           __FILE__, __LINE__);
+            (void)cudaGetLastError();  // do not let a later launch check report this failure
             return TB_ERR_CUDA;
         }
         g_scratch_ptr[device] = p;
@@ -48,12 +51,17 @@ extern "C" int tb_project_static(int device, void* stream, const void* grads, in
                                  int64_t F, int64_t ld, float* out, int64_t ld_out, uint32_t N,
                                  uint32_t seed, uint32_t num_feature_tiles, int proj_type, float alpha,
                                  int accumulate) {
-    // Shapes whose scratch does not fit the fixed array are refused up front.  (Invalid
-    // shapes give a need of 0 here and are rejected by tb_project's own checks below.)
+    // Same argument rules and codes as tb_project, checked before the device is touched.
+    int rc = tb::validate_project_args(grads, dtype, B, F, ld, out, ld_out, N, num_feature_tiles, proj_type);
+    if (rc != TB_OK) return rc;
+    // Shapes whose scratch does not fit the fixed array are refused up front.
     const size_t need = tb_project_workspace_bytes(dtype, B, F, N, num_feature_tiles);
     if (need > tb::STATIC_SCRATCH_BYTES) return TB_ERR_SCRATCH_LIMIT;
+    // Makes `device` current and refuses anything that is not a B200-class GPU.
+    rc = tb::select_device(device, nullptr);
+    if (rc != TB_OK) return rc;
     void* scratch = nullptr;
-    const int rc = tb::scratch_address(device, &scratch);
+    rc = tb::scratch_address(device, &scratch);
     if (rc != TB_OK) return rc;
     // Every scratch byte the kernels read (staged gradients including their zero padding,
     // partial sums) is written earlier in the same call, so nothing has to start at zero

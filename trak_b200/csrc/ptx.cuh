@@ -16,7 +16,6 @@ enum : uint32_t {
     ST_TIMEOUT_FULL_A = 2,  // MMA issuer waited for a generated tile
     ST_TIMEOUT_FULL_B = 3,  // MMA issuer waited for a TMA tile
     ST_TIMEOUT_ACC = 4,     // epilogue waited for the accumulator
-    ST_TIMEOUT_DRAIN = 5,   // teardown waited for copies in flight
     ST_NOT_SPD = 6,         // Cholesky met a non-positive pivot (not a wait: the matrix is not SPD)
 };
 
@@ -93,6 +92,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
@@ -176,6 +183,24 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
            (2ull << 61);
+}
+
+// K-major tile, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart (a TMA box with
+// CU_TENSOR_MAP_SWIZZLE_64B and a 64-byte inner extent, or generic stores that put the 16-byte
+// piece c of row r at piece position c ^ ((r >> 1) & 3)).
+__device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (32ull << 32) | (1ull << 46) |
+           (4ull << 61);
+}
+
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the async proxy
+// (tensor-core operand reads, TMA) before a barrier hands the buffer over.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
 }
 
 // Instruction descriptor for kind::f16 with fp32 accumulation, both operands

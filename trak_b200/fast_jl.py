@@ -4,7 +4,8 @@ Same six callables with the same positional signature
 ``(input, N, seed, num_feature_tiles) -> float32 CUDA tensor [B, N]``
 (fast_jl/fast_jl.cu:81-110), backed by the sm_100a kernels behind the C ABI.
 The 8 / 16 / 32 suffix (rows per launch in the reference) is only a name here:
-every entry point takes any number of rows and walks the matrix once per 256.
+every entry point takes any number of rows; one generation of the matrix serves up to 256 rows
+(Rademacher) or 512 rows (Gaussian) of the batch.
 
 To make an unmodified ``trak`` pick this module up::
 
@@ -20,6 +21,7 @@ from . import _lib
 _STRICT = os.environ.get("TRAK_B200_STRICT", "1") != "0"
 _DTYPES = {torch.float16: _lib.TB_F16, torch.bfloat16: _lib.TB_BF16, torch.float32: _lib.TB_F32}
 _workspaces = {}
+_MAX_CACHED_WORKSPACES = 8  # per process; streams come and go, their workspaces should not pile up
 
 
 def _u32(name, v):
@@ -35,11 +37,12 @@ def _u32(name, v):
 
 def _workspace(device, stream, nbytes):
     key = (device.index, stream)
-    ws = _workspaces.get(key)
+    ws = _workspaces.pop(key, None)
     if ws is None or ws.numel() < nbytes:
-        _workspaces.pop(key, None)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    _workspaces[key] = ws  # most recently used last
+    while len(_workspaces) > _MAX_CACHED_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))
     return ws
 
 

@@ -50,6 +50,8 @@ def vectorize(g: dict, device="cuda") -> torch.Tensor:
 
 
 def _segmentable(vals, device) -> bool:
+    if not vals:
+        return False
     d = torch.device(device)
     return all(v.is_cuda and v.device == d and v.dtype == vals[0].dtype for v in vals) and \
         vals[0].dtype in (torch.float16, torch.bfloat16, torch.float32)
@@ -86,7 +88,9 @@ class CudaProjector:
 
     def project(self, grads: Union[dict, torch.Tensor], model_id: int, *, alpha: float = 1.0,
                 out: torch.Tensor = None, accumulate: bool = False) -> torch.Tensor:
-        seed = (self.seed + int(1e4) * model_id) & 0xFFFFFFFF
+        # the kernel's seed is an unsigned 32-bit integer: a value outside that range raises TypeError,
+        # as the reference's pybind signature does (fast_jl/fast_jl.cu:81-110)
+        seed = self.seed + int(1e4) * model_id
         if isinstance(grads, dict):
             vals = list(grads.values())
             if _segmentable(vals, self.device):
@@ -145,18 +149,28 @@ class ChunkedCudaProjector:
         for p in vals:
             w = 1 if p.dim() < 2 else p[0].numel()
             if width + w > self.max_chunk_size:
-                assert width == self.params_per_chunk[index]
+                self._check_chunk(index, width)
                 self.projector_per_chunk[index].project(dict(enumerate(chunk)), model_id, out=out,
                                                         accumulate=index > 0)
                 chunk, width, index = [], 0, index + 1
             chunk.append(p[:rows])
             width += w
-        assert width == self.params_per_chunk[index]
+        self._check_chunk(index, width)
         self.projector_per_chunk[index].project(dict(enumerate(chunk)), model_id, out=out, accumulate=index > 0)
         return out.to(self.dtype)
 
+    def _check_chunk(self, index, width):
+        """A chunk must hold at least one whole parameter.  ``get_parameter_chunk_sizes`` emits a leading
+        chunk of width 0 when the first parameter alone exceeds the cap (trak/utils.py:321-326); such a
+        chunk cannot be projected, so the cap has to be raised to admit the largest parameter."""
+        if width == 0:
+            raise ValueError(f"parameter chunk {index} is empty: a single parameter is larger than "
+                             f"max_chunk_size={self.max_chunk_size}; raise the chunk size to at least the largest "
+                             "parameter")
+        assert width == self.params_per_chunk[index], "params_per_chunk does not match grads"
+
     def _flush(self, index, rows, pointer, model_id, out, first):
-        assert pointer == self.params_per_chunk[index]
+        self._check_chunk(index, pointer)
         proj = self.projector_per_chunk[index]
         chunk = self.ch_input[:rows, :pointer]
         if isinstance(proj, CudaProjector):
@@ -168,7 +182,10 @@ class ChunkedCudaProjector:
 
     def project(self, grads, model_id):
         vals = list(grads.values())
-        rows = min(self.feat_bs, vals[0].shape[0])
+        rows = vals[0].shape[0]
+        if rows > self.feat_bs:
+            # the reference fails here on the shape mismatch of its copy into ch_input (trak/projectors.py:501-502)
+            raise RuntimeError(f"batch of {rows} gradients exceeds feat_bs={self.feat_bs} of this projector")
         out = torch.empty((rows, self.proj_dim), device=self.device, dtype=torch.float32)
         if all(isinstance(p, CudaProjector) for p in self.projector_per_chunk) and \
                 _segmentable(vals, self.device):
@@ -187,3 +204,45 @@ class ChunkedCudaProjector:
             pointer += width
         self._flush(index, rows, pointer, model_id, out, first)
         return out.to(self.dtype)
+
+
+def get_parameter_chunk_sizes(model_or_widths, batch_size: int = None, max_chunk_size: int = None):
+    """``(max_chunk_size, params_per_chunk)`` as the reference computes them (trak/utils.py:297-331): the
+    parameters, in order, are grouped whole into chunks, a new chunk starting when the running width would
+    reach ``max_chunk_size``.  The reference's cap is ``uint32 max // batch_size`` (its kernel indexes the
+    batch with 32 bits); these kernels have no such limit, so any ``max_chunk_size`` may be given instead.
+    ``model_or_widths`` is a module or the list of parameter widths.  A parameter wider than the cap leaves an
+    empty leading chunk, exactly as in the reference -- raise the cap to at least the widest parameter."""
+    import numpy as np
+    if isinstance(model_or_widths, torch.nn.Module):
+        widths = [p.numel() for p in model_or_widths.parameters()]
+    else:
+        widths = [int(w) for w in model_or_widths]
+    if max_chunk_size is None:
+        if not batch_size:
+            raise ValueError("give batch_size (the reference's rule) or max_chunk_size")
+        max_chunk_size = int(np.iinfo(np.uint32).max // batch_size)
+    chunk_sum, params_per_chunk = 0, []
+    for w in widths:
+        if chunk_sum + w >= max_chunk_size:
+            params_per_chunk.append(chunk_sum)
+            chunk_sum = 0
+        chunk_sum += w
+    rest = sum(widths) - sum(params_per_chunk)
+    if rest > 0:
+        params_per_chunk.append(rest)
+    return max_chunk_size, params_per_chunk
+
+
+def make_chunked_projector(model_or_widths, proj_dim: int, proj_seed: int, feat_bs: int, device, dtype,
+                           max_chunk_size: int = None) -> ChunkedCudaProjector:
+    """The ``ChunkedCudaProjector`` that ``TRAKer.init_projector`` builds (trak/traker.py:284-320): one
+    Rademacher ``CudaProjector`` per chunk with seeds ``default_rng(proj_seed).integers(0, 500, n_chunks)``."""
+    import numpy as np
+    cap, sizes = get_parameter_chunk_sizes(model_or_widths, batch_size=feat_bs, max_chunk_size=max_chunk_size)
+    seeds = np.random.default_rng(proj_seed).integers(low=0, high=500, size=len(sizes))
+    projs = [CudaProjector(grad_dim=int(s), proj_dim=proj_dim, seed=int(sd), proj_type=ProjectionType.rademacher,
+                           device=device, max_batch_size=feat_bs) for s, sd in zip(sizes, seeds) if s > 0]
+    if len(projs) != len(sizes):
+        raise ValueError(f"a parameter is wider than max_chunk_size={cap}; raise it to at least the widest parameter")
+    return ChunkedCudaProjector(projs, cap, sizes, feat_bs, torch.device(device), dtype)

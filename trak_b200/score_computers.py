@@ -28,15 +28,17 @@ from . import _lib
 
 _DTYPES = {torch.float16: _lib.TB_F16, torch.bfloat16: _lib.TB_BF16, torch.float32: _lib.TB_F32}
 _workspaces = {}
+_MAX_CACHED_WORKSPACES = 8  # per process; streams come and go, their workspaces should not pile up
 
 
 def _workspace(device, stream, nbytes):
     key = (device.index, stream)
-    ws = _workspaces.get(key)
+    ws = _workspaces.pop(key, None)
     if ws is None or ws.numel() < nbytes:
-        _workspaces.pop(key, None)
         ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    _workspaces[key] = ws  # most recently used last
+    while len(_workspaces) > _MAX_CACHED_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))
     return ws
 
 
@@ -140,8 +142,13 @@ class B200ScoreComputer:
         self.proj_dim = grads.shape[1]
         acc = None
         for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
+            if block.shape[0] == 0:
+                continue
             blk = _as_device_matrix(block, self.device)
             acc = gram(blk, out=acc, accumulate=acc is not None)
+        if acc is None:
+            # a rank whose shard holds no rows still has to reach the all-reduce: it contributes zeros
+            acc = torch.zeros(self.proj_dim, self.proj_dim, dtype=torch.float32, device=self.device)
         acc = reduce_gram(acc, self.process_group)
         _lib.device_status(self.device.index)
         return acc.to(self.dtype)
@@ -154,9 +161,14 @@ class B200ScoreComputer:
         result = torch.empty(grads.shape[0], inv.shape[1], dtype=self.dtype, device=self.device)
         start = 0
         for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
+            if block.shape[0] == 0:
+                continue
             blk = _as_device_matrix(block, self.device)
+            if blk.dtype != inv.dtype:  # the narrower operand is promoted, never the inverse demoted
+                wide = torch.promote_types(blk.dtype, inv.dtype)
+                blk, inv = blk.to(wide), inv.to(wide)
             # the inverse is symmetric, so block @ inv == block @ inv.T
-            result[start:start + blk.shape[0]] = gemm_nt(blk, inv.to(blk.dtype)).to(self.dtype)
+            result[start:start + blk.shape[0]] = gemm_nt(blk, inv).to(self.dtype)
             start += blk.shape[0]
         _lib.device_status(self.device.index)
         return result
