@@ -60,7 +60,7 @@ BLOCK = 100  # BasicProjector's column block (trak/projectors.py:229)
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the three launches of one projection call on
 # the full workload, from the ncu capture summarised in profiles/project_kernel_normal_bench.md: taken at D/10
 # (traffic grows in proportion to D) and multiplied by 10.
-NCU_TRAFFIC_BYTES_FULL = {"stage_kernel": 5.73e9, "project_kernel": 3.51e9, "reduce_kernel": 0.08e9}
+NCU_TRAFFIC_BYTES_FULL = {"stage_kernel": 5.30e9, "project_kernel": 3.45e9, "reduce_kernel": 0.78e9}
 
 
 def measured_peaks():
@@ -1019,6 +1019,7 @@ def run_ours(args, D):
 
 
 def main():
+    global ROWS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -1027,6 +1028,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of D (profiler captures)")
     ap.add_argument("--proj-type", choices=["normal", "rademacher"], default="normal",
                     help="normal = the benchmark workload; rademacher for profiling the other matrix type")
+    ap.add_argument("--rows", type=int, default=ROWS,
+                    help="rows per GPU (128 = the benchmark workload; other values for profiling other kernel shapes)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-featurize", action="store_true",
                     help="skip the featurize-step measurement (thousands of small PyTorch launches: slow under a profiler)")
@@ -1036,6 +1039,7 @@ def main():
     ap.add_argument("--no-scoring", action="store_true",
                     help="skip the after-kernel scoring and the featurize-step measurements")
     args = ap.parse_args()
+    ROWS = args.rows
     D = max(1024, int(D_FULL * args.scale))
     if args.impl == "reference":
         run_reference(args, D)

@@ -238,3 +238,59 @@ def test_feature_writer_fills_the_stores_like_featurize(cuda, tmp_path):
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-3 if dtype == torch.float16 else 1e-6, atol=1e-6)
         assert torch.equal(torch.from_numpy(np.array(ws)), o2l.to(dtype).cpu())
         assert torch.equal(fw.features_device.cpu(), got)
+
+
+def test_cifar_featurize_slice_with_stores_and_out_to_loss(cuda, tmp_path):
+    """A slice of the 50,000-image featurize job as bench.py runs it: 64 synthetic images, per-example margin
+    gradients of the CIFAR ResNet-18, FeatureWriter (projection with 1/sqrt(D) folded in -> grads.mmap rows,
+    margin out-to-loss weights beside them, trak/traker.py:424-437, trak/modelout_functions.py:153-179).
+    Every stored row is checked on eight 32-column groups against the fp64 oracle."""
+    torchvision = pytest.importorskip("torchvision")
+    from torch.func import functional_call, grad, vmap
+    from trak_b200 import mmap_io
+    from trak_b200.featurize import FeatureWriter
+    from trak_b200.projectors import CudaProjector, ProjectionType, vectorize
+    torch.manual_seed(0)
+    model = torchvision.models.resnet18(num_classes=10)
+    model.conv1 = torch.nn.Conv2d(3, 64, 3, 1, 1, bias=False)
+    model.maxpool = torch.nn.Identity()
+    model = model.to(cuda).eval()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    buffers = {k: v.detach() for k, v in model.named_buffers()}
+    D = sum(p.numel() for p in params.values())
+    n, bs, N = 64, 24, 2048
+    g = torch.Generator().manual_seed(3)
+    xs, ys = torch.rand(n, 3, 32, 32, generator=g).to(cuda), torch.randint(0, 10, (n,), generator=g).to(cuda)
+
+    def margin(p, x, y):
+        logits = functional_call(model, (p, buffers), (x.unsqueeze(0),))[0]
+        own = torch.arange(logits.numel(), device=logits.device) == y
+        rest = torch.logsumexp(torch.where(own, torch.full_like(logits, -torch.inf), logits), 0)
+        return (logits * own).sum() - rest
+
+    per_sample = vmap(grad(margin), in_dims=(None, 0, 0))
+    gs = mmap_io.create_store(tmp_path / "0" / "grads.mmap", (n, N), torch.float32)
+    ws = mmap_io.create_store(tmp_path / "0" / "out_to_loss.mmap", (n, 1), torch.float32)
+    proj = CudaProjector(D, N, 0, ProjectionType.rademacher, cuda, 32)
+    fw = FeatureWriter(proj, D ** 0.5, torch.float32, cuda, max_batch=bs, grads_store=gs, out_to_loss_store=ws, slots=2)
+    flats, weights = [], []
+    for i in range(0, n, bs):          # 24 + 24 + 16 rows
+        x, y = xs[i:i + bs], ys[i:i + bs]
+        grads = per_sample(params, x, y)
+        with torch.no_grad():
+            ps = torch.softmax(model(x), dim=-1)[torch.arange(x.shape[0], device=cuda), y]
+        fw.add(grads, np.arange(i, i + x.shape[0]), model_id=0, loss_grads=(1.0 - ps).unsqueeze(-1))
+        flats.append(vectorize(grads, device=cuda).cpu())
+        weights.append((1.0 - ps).cpu())
+    fw.flush()
+    stored = np.array(mmap_io.open_store(tmp_path / "0" / "grads.mmap", mode="r"), dtype=np.float64)
+    flat = torch.cat(flats).numpy()
+    groups = [0, 9, 17, 26, 35, 44, 53, 63]
+    want = o.project_column_groups(o.RADEMACHER, flat, 0, proj.num_sms, groups, round_f16=True) / D ** 0.5
+    cols = np.concatenate([np.arange(32 * c, 32 * c + 32) for c in groups])
+    rel = np.linalg.norm(stored[:, cols] - want, axis=1) / np.linalg.norm(want, axis=1)
+    print("featurize slice: worst of 64 stored rows on 256 columns against the fp64 oracle:", rel.max())
+    assert rel.max() <= 1e-3, rel
+    w_stored = np.array(mmap_io.open_store(tmp_path / "0" / "out_to_loss.mmap", mode="r"))
+    assert np.array_equal(w_stored[:, 0], torch.cat(weights).numpy())
+    assert (w_stored > 0).all() and (w_stored < 1).all()

@@ -46,6 +46,35 @@ def test_gram_all_reduce_two_ranks(tmp_path):
         torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
 
 
+def _worker_empty_shard(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        X = torch.randn(1, 8, generator=torch.Generator().manual_seed(9))   # one train row, two ranks
+        lo, hi = shard_rows(X.shape[0], rank, world)
+        # a rank without rows contributes a zero Gram and still joins the reduction (what get_xtx does)
+        local = X[lo:hi].T @ X[lo:hi] if hi > lo else torch.zeros(8, 8)
+        total = reduce_gram(local.clone(), dist.group.WORLD)
+        torch.save((hi - lo, total), os.path.join(tmp, f"gram_{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_with_an_empty_shard_still_joins_the_reduction(tmp_path):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker_empty_shard, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    X = torch.randn(1, 8, generator=torch.Generator().manual_seed(9))
+    sizes = []
+    for r in range(2):
+        n, got = torch.load(os.path.join(tmp_path, f"gram_{r}.pt"))
+        sizes.append(n)
+        torch.testing.assert_close(got, X.T @ X)
+    assert sorted(sizes) == [0, 1]
+
+
 def test_reduce_gram_single_process_is_identity():
     g = torch.eye(3)
     assert reduce_gram(g, None) is g

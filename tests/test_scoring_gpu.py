@@ -312,3 +312,20 @@ def test_inverse_at_8192_against_an_fp64_inverse(cuda):
     assert err <= 2e-5, err
     inv2 = sc.spd_inverse_(A32.clone(), lam, rescale=True)
     assert rel(inv2, ref / ref.abs().mean()) <= 2e-5
+
+
+def test_empty_row_block_contributes_a_zero_gram(cuda):
+    """A rank whose shard holds no train rows (fewer rows than ranks) must still return a Gram, so that it
+    reaches the all-reduce its peers are waiting in."""
+    from trak_b200.score_computers import B200ScoreComputer
+    sc = B200ScoreComputer(dtype=torch.float32, device=cuda, lambda_reg=1.0)
+    g = sc.get_xtx(torch.zeros(0, 64))
+    assert g.shape == (64, 64) and float(g.abs().sum()) == 0.0
+    f = sc.get_x_xtx_inv(torch.zeros(0, 64), torch.eye(64))
+    assert f.shape == (0, 64)
+    # 16-bit gradients with an fp32 score computer: the block is promoted, the inverse keeps its precision
+    X = torch.randn(500, 64, generator=torch.Generator().manual_seed(0)).half()
+    gram = sc.get_xtx(X)
+    feats = sc.get_x_xtx_inv(X, gram)
+    ref = br.x_xtx_inv(X.float(), br.xtx(X.float()), 1.0)
+    assert feats.dtype == torch.float32 and rel(feats, ref) <= 1e-4
