@@ -439,6 +439,59 @@ def run_scoring_e2e(dev, rank, world):
     return out
 
 
+def scoring_reference_on_gpu(dev):
+    """The reference's own GPU path for the same three steps: the unmodified BasicScoreComputer(device="cuda")
+    (torch.matmul / torch.linalg.inv, i.e. cuBLAS and cuSOLVER in fp32, trak/score_computers.py:145-189) on one
+    131,072-row shard of the C4 job, next to this library on the very same tensors.  Outside every timed region of
+    the benchmark; needs the reference package (baseline/_ref)."""
+    import torch
+    trak = reference_package()
+    if trak is None:
+        return {"unavailable": "reference package not installed under baseline/_ref"}
+    from trak_b200.score_computers import B200ScoreComputer
+    n, k, m = 131_072, SC_K, SC_M
+    gen = torch.Generator(device=dev).manual_seed(2000)
+    X = torch.empty(n, k, device=dev)
+    for i in range(0, n, SC_BLOCK):
+        X[i:i + SC_BLOCK] = torch.randn(min(SC_BLOCK, n - i), k, device=dev, generator=gen) / k ** 0.5
+    T = torch.randn(m, k, device=dev, generator=torch.Generator(device=dev).manual_seed(3000)) / k ** 0.5
+    ref = trak.score_computers.BasicScoreComputer(dtype=torch.float32, device=dev, logging_level=40,
+                                                  lambda_reg=SC_LAMBDA)
+    mine = B200ScoreComputer(torch.float32, dev, lambda_reg=SC_LAMBDA)
+
+    acc = torch.zeros(n, m)   # on the host, where TRAKer keeps it and the reference's get_scores needs it
+
+    def run(sc):
+        acc.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        g = sc.get_xtx(X)
+        f = sc.get_x_xtx_inv(X, g)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        sc.get_scores(f, T, acc)
+        torch.cuda.synchronize()
+        return t1 - t0, time.perf_counter() - t1
+
+    run(mine)
+    mine_dev, mine_scores = run(mine)
+    s_mine = acc[:4096].clone()
+    run(ref)
+    ref_dev, ref_scores = run(ref)
+    diff = float((s_mine - acc[:4096]).norm() / acc[:4096].norm())
+    del X
+    torch.cuda.empty_cache()
+    return {"reference_seconds": ref_dev + ref_scores, "this_library_seconds": mine_dev + mine_scores,
+            "ratio": (ref_dev + ref_scores) / (mine_dev + mine_scores),
+            "gram_inverse_features": {"reference_seconds": ref_dev, "this_library_seconds": mine_dev},
+            "scores_into_host_accumulator": {"reference_seconds": ref_scores, "this_library_seconds": mine_scores},
+            "relative_difference_of_scores": diff,
+            "what": f"get_xtx + get_x_xtx_inv + get_scores on device-resident X fp32 [{n} x {k}], {m} targets, host "
+                    "accumulator (wall clock): the reference's unmodified BasicScoreComputer(device='cuda') -- "
+                    "cuBLAS fp32 products, cuSOLVER LU inverse, a pageable copy of the scores -- against "
+                    "B200ScoreComputer on the same tensors"}
+
+
 def scoring_cpu_baseline(threads, dev=None):
     """The reference's BasicScoreComputer on the host cores on a bounded sample (k full, fewer rows and targets),
     scaled to C4 -- and, with `dev`, this library on the very same sample, compared with it (``parity``)."""
@@ -812,6 +865,9 @@ def run_ours(args, D):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # torchrun starts every rank with OMP_NUM_THREADS=1; the host side of the end-to-end legs (adding score
+        # blocks into the host accumulator, writing store rows) gets this rank's share of the host cores instead
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     lib = _lib.lib()
 
     ptype = _lib.TB_NORMAL if args.proj_type == "normal" else _lib.TB_RADEMACHER
@@ -946,6 +1002,8 @@ def run_ours(args, D):
 
     if scoring is not None and extras and args.scale == 1.0:
         scoring["e2e"] = guarded(run_scoring_e2e, dev, rank, world)
+        if world == 1:
+            scoring["reference_on_gpu"] = guarded(scoring_reference_on_gpu, dev)
     do_feat = not (args.no_scoring or args.no_featurize)
     featurize = guarded(run_featurize, dev, rank, world) if do_feat else None
     featurize_job = guarded(run_featurize_job, dev, rank, world) if (do_feat and extras) else None

@@ -347,6 +347,23 @@ def test_full_benchmark_shape_all_rows_against_the_reference_kernel(cuda):
         print(f"{name}: 120 random rows against the reference kernel, worst row {err:.2e}")
         assert err <= TOL, (name, err)
         del got, ref
+        # the same launch timed on both (CUDA events on the current stream, 3 calls after a warm-up each; the
+        # reference kernel runs on the legacy default stream, which the current stream synchronises with)
+        ms = {}
+        for who, fn in (("ours", lambda: ours(g, N, seed, T, p, strict=False)),
+                        ("reference", lambda: getattr(w, f"project_{name}_32")(g, N, seed, T))):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms[who] = e0.elapsed_time(e1) / 3
+        print(f"{name}, 128 x 11,173,962 -> 4096: reference fast_jl kernel {ms['reference']:.1f} ms, "
+              f"this library {ms['ours']:.1f} ms ({ms['reference'] / ms['ours']:.1f}x)")
+        assert ms["reference"] >= 3.0 * ms["ours"], ms
 
 
 WIDE_SHAPES = [  # B, F, N, seed, tiles, dtype: batches that take the 512-row Gaussian kernel
