@@ -10,7 +10,8 @@
 // fence.proxy.async + an mbarrier; both MMA operands then come from shared memory.
 //
 //   * WIDE_NG generator groups of four warps, one CTA per SM; group g walks feature tiles
-//     g, g + WIDE_NG, ... of the CTA's bundle, 32 features per slot, two slots per group
+//     g, g + WIDE_NG, ... of the CTA's bundle, 32 features per slot, two slots per group; most bundles
+//     hold WIDE_NG tiles, the last ones fewer so that the grid's last wave fills the SMs
 //   * the gradient stream is ONE ring shared by all groups: the MMA warp consumes blocks in a
 //     fixed round-robin order (which also fixes the summation order), and the TMA warp loads the
 //     [Bpad x 32] boxes in that same order, so the ring holds the next few blocks whoever owns them
@@ -51,8 +52,12 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
     const uint32_t b_ring = smem_base + WIDE_A_RING;
 
     const uint32_t col0 = blockIdx.x * 128u;
-    const uint32_t tile0 = blockIdx.y * p.tiles_per_bundle;
-    const uint32_t ntile = min(p.tiles_per_bundle, p.tiles - tile0);
+    // the first bundles_a bundles hold tiles_per_bundle tiles each, the ones behind them tiles_per_bundle_b
+    const bool big = blockIdx.y < p.bundles_a;
+    const uint32_t tpb = big ? p.tiles_per_bundle : p.tiles_per_bundle_b;
+    const uint32_t tile0 = big ? blockIdx.y * p.tiles_per_bundle
+                               : p.bundles_a * p.tiles_per_bundle + (blockIdx.y - p.bundles_a) * p.tiles_per_bundle_b;
+    const uint32_t ntile = min(tpb, p.tiles - tile0);
 
     if (threadIdx.x == 0) {
         for (uint32_t g = 0; g < NG; ++g)
