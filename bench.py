@@ -296,28 +296,45 @@ def run_scoring(args, dev, rank, world, scale):
     gram = torch.empty(k, k, device=dev)
     group = dist.group.WORLD if world > 1 else None
 
-    def job():
-        for i in range(0, n, SC_BLOCK):
-            sc.gram(X[i:i + SC_BLOCK], out=gram, accumulate=i > 0)
+    # Row blocks alternate between two streams (score_computers.StreamPair), as B200ScoreComputer runs them: the
+    # memory-bound packing passes of one block overlap the tensor-bound GEMM of the other.  Each stream has its own
+    # partial Gram and its own features buffer.
+    pair = sc.StreamPair(dev)
+    gram2 = torch.empty(k, k, device=dev)
+    feats2 = torch.empty_like(feats)
+    grams, fbuf = [gram, gram2], [feats, feats2]
+    starts = list(range(0, n, SC_BLOCK))
+
+    def gram_phase():
+        with pair:
+            for j, i in enumerate(starts):
+                with pair.stream(j):
+                    sc.gram(X[i:i + SC_BLOCK], out=grams[j % 2], accumulate=j >= 2)
+        if len(starts) > 1:
+            gram.add_(gram2)
         sc.reduce_gram(gram, group)                     # the one exchange of the path (NCCL all-reduce)
         sc.spd_inverse_(gram, SC_LAMBDA, rescale=True)  # gram now holds the rescaled inverse
-        for i in range(0, n, SC_BLOCK):
-            rows = min(SC_BLOCK, n - i)
-            sc.gemm_nt(X[i:i + rows], gram, out=feats[:rows])
-            sc.gemm_nt(feats[:rows], T, out=scores[i:i + rows], row_scale=w[i:i + rows])
+
+    def job():
+        gram_phase()
+        with pair:
+            for j, i in enumerate(starts):
+                rows = min(SC_BLOCK, n - i)
+                with pair.stream(j):
+                    sc.gemm_nt(X[i:i + rows], gram, out=fbuf[j % 2][:rows])
+                    sc.gemm_nt(fbuf[j % 2][:rows], T, out=scores[i:i + rows], row_scale=w[i:i + rows])
 
     solved = torch.empty(m, k, device=dev)
 
     def job_direct():
         # the same scores without the features: targets through the inverse first, one product over the rows
-        for i in range(0, n, SC_BLOCK):
-            sc.gram(X[i:i + SC_BLOCK], out=gram, accumulate=i > 0)
-        sc.reduce_gram(gram, group)
-        sc.spd_inverse_(gram, SC_LAMBDA, rescale=True)
+        gram_phase()
         sc.gemm_nt(T, gram, out=solved)
-        for i in range(0, n, SC_BLOCK):
-            rows = min(SC_BLOCK, n - i)
-            sc.gemm_nt(X[i:i + rows], solved, out=scores[i:i + rows], row_scale=w[i:i + rows])
+        with pair:
+            for j, i in enumerate(starts):
+                rows = min(SC_BLOCK, n - i)
+                with pair.stream(j):
+                    sc.gemm_nt(X[i:i + rows], solved, out=scores[i:i + rows], row_scale=w[i:i + rows])
 
     def barrier():
         if world > 1:
@@ -349,7 +366,7 @@ def run_scoring(args, dev, rank, world, scale):
     out = {"metric": "scoring_seconds", "value": sec, "unit": "s", "higher_is_better": False, "scaling": "strong",
            "config": {"workload": f"C4 scoring: X fp32 [{n_total} x {k}] N(0,1/k) sharded by rows over {world} GPU(s), "
                                   f"lambda {SC_LAMBDA}, {m} targets, out-to-loss weights fused",
-                      "row_block": SC_BLOCK,
+                      "row_block": SC_BLOCK, "streams": "row blocks alternate between two streams",
                       "ordering": "the reference's: Gram, inverse, features X.inv, scores features.targets^T"},
            "algorithmic_tflops": scoring_flop(n_total, k, m) / sec / 1e12,
            "roofline": {"bound": "tensor", "achieved": scoring_flop(n_total, k, m) / sec / 1e12 / world, "peak": peak,
@@ -367,7 +384,7 @@ def run_scoring(args, dev, rank, world, scale):
         # Gram by itself, inverts it and recomputes its first 256 rows of scores; the sharded job's all-reduce adds
         # the same partial Grams in another order, so the two agree to fp32 round-off.
         x256, w256 = X[:256].clone(), w[:256].clone()
-        del X, feats
+        del X, feats, feats2, fbuf
         torch.cuda.empty_cache()
         if rank == 0:
             g1 = torch.empty(k, k, device=dev)
@@ -387,7 +404,7 @@ def run_scoring(args, dev, rank, world, scale):
                         "score_computers.reduce_gram) against the same rows recomputed by rank 0 alone from all shards"}
         dist.barrier()
     else:
-        del X, feats
+        del X, feats, feats2, fbuf
     del scores
     torch.cuda.empty_cache()
     return out

@@ -46,6 +46,34 @@ def free_workspaces():
     _workspaces.clear()
 
 
+class StreamPair:
+    """Two side streams that row blocks alternate between.  Every product here is a memory-bound packing pass
+    (row maxima, fp16 hi / lo planes) followed by a tensor-core GEMM; on one stream the packing of block i + 1
+    waits for the GEMM of block i although the two use different parts of the SM.  With blocks alternating
+    between two streams the packing (and any host-to-device copy) of one block runs under the GEMM of the other.
+    Inside ``with pair:`` the side streams first wait for the caller's stream, and the caller's stream waits for
+    both on exit; ``with pair.stream(i):`` makes stream ``i % 2`` current.  Work that touches the same memory
+    from consecutive blocks (an accumulator, a reused buffer) must be given one buffer per stream."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.streams = [torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)]
+
+    def __enter__(self):
+        self.main = torch.cuda.current_stream(self.device)
+        for s in self.streams:
+            s.wait_stream(self.main)
+        return self
+
+    def __exit__(self, *exc):
+        for s in self.streams:
+            self.main.wait_stream(s)
+        return False
+
+    def stream(self, i: int):
+        return torch.cuda.stream(self.streams[i % 2])
+
+
 def _as_device_matrix(t: torch.Tensor, device) -> torch.Tensor:
     t = t.to(device, non_blocking=True)
     if t.dtype not in _DTYPES:
@@ -140,15 +168,23 @@ class B200ScoreComputer:
     # -- trak/score_computers.py:145-155
     def get_xtx(self, grads: torch.Tensor) -> torch.Tensor:
         self.proj_dim = grads.shape[1]
-        acc = None
-        for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
-            if block.shape[0] == 0:
-                continue
-            blk = _as_device_matrix(block, self.device)
-            acc = gram(blk, out=acc, accumulate=acc is not None)
+        accs = [None, None]   # one partial Gram per stream of the pair (blocks alternate between them)
+        with torch.cuda.device(self.device), self._pair() as pair:
+            for i, block in enumerate(b for b in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0) if b.shape[0]):
+                with pair.stream(i):
+                    blk = _as_device_matrix(block, self.device)
+                    blk.record_stream(torch.cuda.current_stream(self.device))
+                    accs[i % 2] = gram(blk, out=accs[i % 2], accumulate=accs[i % 2] is not None)
+        main = torch.cuda.current_stream(self.device)
+        for a in accs:   # allocated on a side stream, used on the caller's from here on
+            if a is not None:
+                a.record_stream(main)
+        acc = accs[0]
         if acc is None:
             # a rank whose shard holds no rows still has to reach the all-reduce: it contributes zeros
             acc = torch.zeros(self.proj_dim, self.proj_dim, dtype=torch.float32, device=self.device)
+        elif accs[1] is not None:
+            acc.add_(accs[1])
         acc = reduce_gram(acc, self.process_group)
         _lib.device_status(self.device.index)
         return acc.to(self.dtype)
@@ -159,19 +195,32 @@ class B200ScoreComputer:
         spd_inverse_(inv, self.lambda_reg, rescale=True)
         inv = inv.to(self.dtype)
         result = torch.empty(grads.shape[0], inv.shape[1], dtype=self.dtype, device=self.device)
+        if grads.shape[0]:
+            probe = grads[:1]
+            in_dtype = probe.dtype if probe.dtype in _DTYPES else torch.float32
+            if in_dtype != inv.dtype:  # the narrower operand is promoted, never the inverse demoted
+                inv = inv.to(torch.promote_types(in_dtype, inv.dtype))
         start = 0
-        for block in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0):
-            if block.shape[0] == 0:
-                continue
-            blk = _as_device_matrix(block, self.device)
-            if blk.dtype != inv.dtype:  # the narrower operand is promoted, never the inverse demoted
-                wide = torch.promote_types(blk.dtype, inv.dtype)
-                blk, inv = blk.to(wide), inv.to(wide)
-            # the inverse is symmetric, so block @ inv == block @ inv.T
-            result[start:start + blk.shape[0]] = gemm_nt(blk, inv).to(self.dtype)
-            start += blk.shape[0]
+        with torch.cuda.device(self.device), self._pair() as pair:
+            for i, block in enumerate(b for b in torch.split(grads, self.CUDA_MAX_DIM_SIZE, dim=0) if b.shape[0]):
+                rows = slice(start, start + block.shape[0])
+                start += block.shape[0]
+                with pair.stream(i):
+                    blk = _as_device_matrix(block, self.device).to(inv.dtype)
+                    blk.record_stream(torch.cuda.current_stream(self.device))
+                    # the inverse is symmetric, so block @ inv == block @ inv.T
+                    if result.dtype == torch.float32:
+                        gemm_nt(blk, inv, out=result[rows])
+                    else:
+                        result[rows] = gemm_nt(blk, inv).to(self.dtype)
         _lib.device_status(self.device.index)
         return result
+
+    def _pair(self) -> StreamPair:
+        pair = getattr(self, "_stream_pair", None)
+        if pair is None:
+            self._stream_pair = pair = StreamPair(self.device)
+        return pair
 
     # -- trak/score_computers.py:179-189
     def get_scores(self, features: torch.Tensor, target_grads: torch.Tensor, accumulator: torch.Tensor,
@@ -212,26 +261,31 @@ class B200ScoreComputer:
             accumulator[rows] += buf.to(accumulator.dtype)
 
         start = 0
-        for i, block in enumerate(torch.split(features, step, dim=0)):
-            blk = _as_device_matrix(block, self.device)
-            rs = None if row_scale is None else row_scale.reshape(-1)[start:start + blk.shape[0]]
-            part = gemm_nt(blk, targets, row_scale=rs)
-            rows = slice(start, start + blk.shape[0])
-            start += blk.shape[0]
-            if not on_host:
-                if accumulator.device == part.device:
-                    accumulator[rows] += part.to(accumulator.dtype)
-                else:
-                    accumulator[rows] += part.to(accumulator.dtype).to(accumulator.device)
-                continue
-            # buffer i % 2 was last read by the flush of block i - 2, which has returned
-            buf = stage[i % 2][:blk.shape[0]]
-            buf.copy_(part, non_blocking=True)
-            event = torch.cuda.Event()
-            event.record(torch.cuda.current_stream(self.device))
-            if pending is not None:
-                flush(pending)
-            pending = (rows, buf, event)
+        with torch.cuda.device(self.device), self._pair() as pair:
+            for i, block in enumerate(b for b in torch.split(features, step, dim=0) if b.shape[0]):
+                rows = slice(start, start + block.shape[0])
+                start += block.shape[0]
+                with pair.stream(i):
+                    cur = torch.cuda.current_stream(self.device)
+                    blk = _as_device_matrix(block, self.device)
+                    blk.record_stream(cur)
+                    rs = None if row_scale is None else row_scale.reshape(-1)[rows]
+                    part = gemm_nt(blk, targets, row_scale=rs)
+                    if not on_host:
+                        if accumulator.device == part.device:
+                            accumulator[rows] += part.to(accumulator.dtype)
+                        else:
+                            accumulator[rows] += part.to(accumulator.dtype).to(accumulator.device)
+                        continue
+                    # buffer i % 2 was last read by the flush of block i - 2, which has returned; the copy runs
+                    # on this block's stream, so the GEMM of the next block (other stream) overlaps it
+                    buf = stage[i % 2][:blk.shape[0]]
+                    buf.copy_(part, non_blocking=True)
+                    event = torch.cuda.Event()
+                    event.record(cur)
+                if pending is not None:
+                    flush(pending)
+                pending = (rows, buf, event)
         if pending is not None:
             flush(pending)
         _lib.device_status(self.device.index)
