@@ -981,6 +981,18 @@ def run_ours(args, D):
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = world * ROWS / e2e_t.item()
     assert torch.equal(host_out, out.cpu()), "end-to-end result differs from the resident-input result"
+    # the host-to-device copy of one batch alone, all ranks copying at once: what the end-to-end figure is bound by
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(3):
+        bufs[1].copy_(host_in, non_blocking=True)
+    c1.record()
+    torch.cuda.synchronize()
+    h2d = torch.tensor([3 * ROWS * D * 2 / (c0.elapsed_time(c1) * 1e-3) / 1e9], device=dev)
+    if world > 1:
+        dist.all_reduce(h2d, op=dist.ReduceOp.MIN)
+    h2d_gbs = h2d.item()
     g_stage = bufs[1]
     del host_in, g_stage, bufs
     torch.cuda.empty_cache()
@@ -1050,7 +1062,11 @@ def run_ours(args, D):
                                   "16x32 tile, so the tensor pipe idles") if ptype == _lib.TB_NORMAL
                          else "MMA-bound under the power cap plus the restaging pass"},
             "e2e": {"value": e2e_value, "unit": "examples/s", "h2d_bytes_per_step": ROWS * D * 2,
-                    "d2h_bytes_per_step": ROWS * K_DIM * 4},
+                    "d2h_bytes_per_step": ROWS * K_DIM * 4, "h2d_gb_per_s_per_rank": h2d_gbs,
+                    "h2d_bound_examples_per_s": world * h2d_gbs * 1e9 / (D * 2),
+                    "note": "h2d_gb_per_s_per_rank: the pinned host-to-device copy of a batch timed alone with all "
+                            "ranks copying at once (slowest rank); times the ranks and over the bytes of an example "
+                            "it is the ceiling of the end-to-end figure"},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
         }

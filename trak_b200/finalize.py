@@ -64,7 +64,7 @@ def _rows_to_device(src, lo, hi, device, stager):
 def _whole_to_device(src, device):
     if isinstance(src, torch.Tensor):
         return sc._as_device_matrix(src, device)
-    return sc._as_device_matrix(torch.from_numpy(np.ascontiguousarray(src)), device)
+    return sc._as_device_matrix(torch.from_numpy(np.array(src)), device)   # a copy: the store may be read-only
 
 
 class ScoreFinalizer:
@@ -152,7 +152,7 @@ class ScoreFinalizer:
                         blk, tg = blk.to(wide), tg.to(wide)
                     sc.gemm_nt(blk, tg, out=acc[:nrows], accumulate=j > 0)
                     wj = self.out_to_loss[j]
-                    wj = wj[r0:r1] if isinstance(wj, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(wj[r0:r1]))
+                    wj = wj[r0:r1] if isinstance(wj, torch.Tensor) else torch.from_numpy(np.array(wj[r0:r1]))
                     w_sum += wj.to(dev, torch.float32, non_blocking=True).reshape(-1)
                 finalize_scores_block(acc[:nrows], w_sum, M, out=done[:nrows])
                 # buffer i % 2 was last read by the flush of block i - 2, which has returned
