@@ -85,7 +85,11 @@ int tb_selftest_wait_timeout(int device, void *stream, uint32_t limit_ms);
  *   alpha, accumulate   extras: fold 1/sqrt(D) and sum parameter chunks
  *           without another pass (trak/traker.py:426, trak/projectors.py:490)
  *   ws      workspace of at least tb_project_workspace_bytes(...) bytes,
- *           256-byte aligned; any B is accepted (no 8/16/32 variants)
+ *           256-byte aligned; any B is accepted (no 8/16/32 variants).  The
+ *           batch is walked in passes that each regenerate the matrix once:
+ *           up to 256 rows per pass for TB_RADEMACHER, up to 512 for
+ *           TB_NORMAL (whose generation is what the projection costs), so
+ *           one large call is much cheaper than many small ones
  */
 size_t tb_project_workspace_bytes(int dtype, int64_t B, int64_t F, uint32_t N,
                                   uint32_t num_feature_tiles);
