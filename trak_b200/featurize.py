@@ -64,6 +64,8 @@ class FeatureWriter:
         """Projects one batch of per-sample gradients (dict of tensors or ``[B, D]`` matrix), scales by
         ``1 / normalize_factor`` and queues the rows ``inds`` of the stores.  Returns the fp32 device
         features of the batch (valid until ``slots`` more batches have been added)."""
+        if isinstance(inds, torch.Tensor):
+            inds = inds.detach().cpu().numpy()
         inds = np.asarray(inds).reshape(-1)
         rows = len(inds)
         if rows > self.max_batch:
