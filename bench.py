@@ -645,26 +645,27 @@ def run_featurize(dev, rank, world):
             "ms_per_step": sec.item() * 1e3, "gradients_ms": g_ms / steps, "projection_ms": p_ms / steps}
 
 
-def time_projection(lib, fast_jl, g, ptype, calls=3, warm=1):
-    """(ms per call, ms of the projection kernel alone) of fast_jl.project on a resident batch: CUDA events
-    around the calls on the current stream, and the library's own event pair around the dominant kernel."""
+def time_projection(lib, fast_jl, g, ptype, calls=5, warm=2):
+    """(ms per call, ms of the projection kernel alone) of fast_jl.project on a resident batch: the median over
+    `calls` calls, each between its own pair of CUDA events on the current stream, and the library's own event
+    pair around the dominant kernel (the median keeps the first calls after a clock change out of the figure)."""
     import torch
     out = torch.empty(g.shape[0], K_DIM, device=g.device, dtype=torch.float32)
     for _ in range(warm):
         fast_jl.project(g, K_DIM, SEED, TILES, ptype, out=out, strict=False)
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(calls)]
-    for a, b in kev:
-        a.record()
-        b.record()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(calls)]
+    for quad in ev:
+        for e in quad:
+            e.record()
     torch.cuda.synchronize()
-    e0.record()
-    for a, b in kev:
-        lib.tb_profile_events(a.cuda_event, b.cuda_event)
+    for c0, c1, k0, k1 in ev:
+        c0.record()
+        lib.tb_profile_events(k0.cuda_event, k1.cuda_event)
         fast_jl.project(g, K_DIM, SEED, TILES, ptype, out=out, strict=False)
-    e1.record()
+        c1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / calls, sum(a.elapsed_time(b) for a, b in kev) / calls
+    return (statistics.median(c0.elapsed_time(c1) for c0, c1, _, _ in ev),
+            statistics.median(k0.elapsed_time(k1) for _, _, k0, k1 in ev))
 
 
 def run_rows_sweep(lib, fast_jl, _lib, dev, D, rows_list=(16, 32, 64, 128, 256, 512)):
@@ -678,7 +679,7 @@ def run_rows_sweep(lib, fast_jl, _lib, dev, D, rows_list=(16, 32, 64, 128, 256, 
     big = torch.empty(max(rows_list), D, device=dev, dtype=torch.float16)
     for i in range(0, big.shape[0], 64):  # generated block-wise to bound temporary memory
         big[i:i + 64] = (torch.randn(min(64, big.shape[0] - i), D, device=dev, generator=gen) * 1e-2).half()
-    out = {"rows": list(rows_list), "unit_ms": "ms per call (restage + project + reduce)", "proj_dim": K_DIM, "grad_dim": D}
+    out = {"rows": list(rows_list), "unit_ms": "ms per call (restage + project + reduce), median of 5 calls", "proj_dim": K_DIM, "grad_dim": D}
     for name, ptype in (("normal", _lib.TB_NORMAL), ("rademacher", _lib.TB_RADEMACHER)):
         ms, eps, frac = [], [], []
         for r in rows_list:
@@ -704,7 +705,7 @@ def run_scaling_strong(lib, fast_jl, _lib, g, rank, world):
     for name, ptype in (("normal", _lib.TB_NORMAL), ("rademacher", _lib.TB_RADEMACHER)):
         part = g[rank * rows % ROWS: rank * rows % ROWS + rows]
         dist.barrier()
-        t, _ = time_projection(lib, fast_jl, part, ptype, calls=5, warm=2)
+        t, _ = time_projection(lib, fast_jl, part, ptype, calls=7, warm=3)
         tt = torch.tensor([t], device=g.device)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         res[name] = {"ms_per_call": tt.item(), "examples_per_s": rows * world / tt.item() * 1e3}
@@ -1002,7 +1003,7 @@ def run_ours(args, D):
     if extras:
         oname, otype = ("rademacher", _lib.TB_RADEMACHER) if ptype == _lib.TB_NORMAL else ("normal", _lib.TB_NORMAL)
         barrier()
-        o_ms, o_kernel = time_projection(lib, fast_jl, g, otype, calls=max(3, min(args.steps, 10)), warm=2)
+        o_ms, o_kernel = time_projection(lib, fast_jl, g, otype, calls=max(5, min(args.steps, 10)), warm=3)
         om = torch.tensor([o_ms, o_kernel], device=dev)
         if world > 1:
             dist.all_reduce(om, op=dist.ReduceOp.MAX)
