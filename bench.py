@@ -683,6 +683,7 @@ def run_rows_sweep(lib, fast_jl, _lib, dev, D, rows_list=(16, 32, 64, 128, 256, 
     for name, ptype in (("normal", _lib.TB_NORMAL), ("rademacher", _lib.TB_RADEMACHER)):
         ms, eps, frac = [], [], []
         for r in rows_list:
+            time.sleep(0.25)  # lets the SM clock recover from the previous, possibly power-capped, configuration
             t, _ = time_projection(lib, fast_jl, big[:r], ptype)
             ms.append(round(t, 3))
             eps.append(round(r / t * 1e3, 1))
