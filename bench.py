@@ -1060,7 +1060,7 @@ def run_ours(args, D):
                          "algorithmic_bytes_per_launch": ROWS * D * 2 + ROWS * K_DIM * 4,
                          "kernel": f"project_kernel<{args.proj_type}>", "kernel_ms": kernel_ms,
                          "algorithmic_flop_per_launch": flop, "peak_source": peak_note,
-                         "note": ("generator-issue-bound: the Gaussian matrix costs ~530 instructions per "
+                         "note": ("generator-issue-bound: the Gaussian matrix costs ~470 instructions per "
                                   "16x32 tile, so the tensor pipe idles") if ptype == _lib.TB_NORMAL
                          else "MMA-bound under the power cap plus the restaging pass"},
             "e2e": {"value": e2e_value, "unit": "examples/s", "h2d_bytes_per_step": ROWS * D * 2,
