@@ -118,3 +118,16 @@ def test_finalize_and_featurize_components_need_a_cuda_device():
         ScoreFinalizer([torch.zeros(4, 2)], [torch.zeros(3, 2)], [torch.zeros(4, 1)], "cpu")
     with pytest.raises(ValueError):
         FeatureWriter(_FakeProjector(1), 1.0, torch.float32, "cpu", max_batch=4)
+
+
+def test_install_fast_jl_shim_registers_the_module(monkeypatch):
+    import sys
+    import trak_b200
+    monkeypatch.delitem(sys.modules, "fast_jl", raising=False)
+    trak_b200.install_fast_jl_shim()
+    import fast_jl
+    assert fast_jl is trak_b200.fast_jl
+    for t in ("rademacher", "normal"):
+        for b in (8, 16, 32):
+            assert callable(getattr(fast_jl, f"project_{t}_{b}"))
+    monkeypatch.delitem(sys.modules, "fast_jl", raising=False)
