@@ -392,7 +392,8 @@ def test_wide_gaussian_batches(cuda, B, F, N, seed, T, dt):
     wide = ours(g, N, seed, T, NOR)
     narrow = torch.cat([ours(g[i:i + 200].contiguous(), N, seed, T, NOR) for i in range(0, B, 200)])
     assert torch.equal(wide[hot_rows], narrow[hot_rows])
-    assert rel_rows(wide.cpu().numpy(), narrow.cpu().numpy()) <= 1e-5
+    # both kernels accumulate in the tensor core's truncating fp32, in different orders: about 1e-5 apart
+    assert rel_rows(wide.cpu().numpy(), narrow.cpu().numpy()) <= 1e-4
     assert torch.equal(wide, ours(g, N, seed, T, NOR))            # run-to-run identical
     if B * F * N <= 6e12:
         ref = o.project(NOR, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
@@ -404,6 +405,31 @@ def test_wide_gaussian_batches(cuda, B, F, N, seed, T, dt):
     out = torch.full((B, N), 0.5, device=cuda)
     ours(g, N, seed, T, NOR, alpha=0.25, out=out, accumulate=True)
     torch.testing.assert_close(out, 0.5 + 0.25 * wide, rtol=1e-6, atol=1e-5)
+
+
+def test_randomised_wide_shapes_against_the_narrow_kernel(cuda):
+    """Sixteen seeded random shapes for the 512-row Gaussian kernel (row counts on both sides of a pass, feature
+    counts around tile and stage boundaries, tile counts that leave generator groups idle or give ragged last
+    bundles): the same input through 200-row calls (narrow kernel) must agree to fp32 summation order (the tensor
+    core's accumulation truncates, so two orders differ by about 1e-5), one-hot rows bit for bit."""
+    rng = np.random.default_rng(7)
+    for case in range(16):
+        T = int(rng.choice([1, 2, 6, 7, 8, 13, 37, 108, 148, 149, 500]))
+        F = int(rng.choice([1, 31, 32, 33, 63, 64, 65, 1000, 4097, 9473, 30_011]))
+        N = int(rng.choice([512, 1024, 2560]))
+        B = int(rng.choice([257, 258, 288, 300, 333, 511, 512, 513, 700, 1025]))
+        seed = int(rng.integers(0, 2 ** 32))
+        dt = ["f16", "f32", "bf16"][case % 3]
+        g = (torch.randn(B, F, device=cuda, generator=torch.Generator(device=cuda).manual_seed(case)) * 0.1).to(DT[dt])
+        hot = sorted({0, F - 1, F // 2})
+        rows = [0, 256, B - 1][:len(hot)]
+        for r, f in zip(rows, hot):
+            g[r].zero_()
+            g[r, f] = 1.0
+        wide = ours(g, N, seed, T, NOR)
+        narrow = torch.cat([ours(g[i:i + 200].contiguous(), N, seed, T, NOR) for i in range(0, B, 200)])
+        assert torch.equal(wide[rows], narrow[rows]), (case, T, F, N, B, dt)
+        assert rel_rows(wide.cpu().numpy(), narrow.cpu().numpy()) <= 1e-4, (case, T, F, N, B, dt)
 
 
 def test_wide_gaussian_from_segments(cuda):
