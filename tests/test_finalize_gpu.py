@@ -111,3 +111,29 @@ def test_shapes_are_checked(cuda):
         fin.run(torch.zeros(50, 9))
     with pytest.raises(ValueError):
         fin.run(torch.zeros(50, 8), rows=(10, 60))
+
+
+def test_half_precision_stores_as_traker_writes_them_by_default(cuda, tmp_path):
+    """TRAKer's default dtype is fp16: features.mmap, <exp>_grads.mmap, out_to_loss.mmap and the scores store
+    are all fp16 (trak/traker.py:141, trak/savers.py:363-442).  The finalizer takes them as they are (one-plane
+    tensor-core products, fp32 accumulation over the checkpoints) and writes fp16 scores."""
+    from trak_b200 import mmap_io
+    from trak_b200.finalize import ScoreFinalizer
+    M, n, k, m = 2, 1500, 192, 40
+    feats, targs, o2l = _checkpoints(M, n, k, m, 23)
+    feats, targs, o2l = [f.half() for f in feats], [t.half() for t in targs], [w.half() for w in o2l]
+    f_st, t_st, w_st = [], [], []
+    for j in range(M):
+        for name, src, lst in (("features", feats[j], f_st), ("exp_grads", targs[j], t_st), ("out_to_loss", o2l[j], w_st)):
+            st = mmap_io.create_store(tmp_path / str(j) / f"{name}.mmap", src.shape, torch.float16)
+            st[:] = src.numpy()
+            st.flush()
+            lst.append(mmap_io.open_store(tmp_path / str(j) / f"{name}.mmap", mode="r"))
+    scores = mmap_io.create_store(tmp_path / "scores" / "exp.mmap", (n, m), torch.float16)
+    ScoreFinalizer(f_st, t_st, w_st, cuda, row_block=512).run(scores)
+    got = torch.from_numpy(np.array(scores)).double()
+    S = sum(f.double() @ t.double().T for f, t in zip(feats, targs))
+    w = sum(x.double() for x in o2l)
+    want = (S / M) * (w / M)
+    err = float((got - want).norm() / want.norm())
+    assert err <= 1e-3, err        # fp16 rounding of the stored scores (2^-11 per entry)
