@@ -352,22 +352,35 @@ __global__ void write_diag_inverse_kernel(float* A, int64_t lda, int k, const fl
         if (i < jb && j < jb) A[(int64_t)(j0 + i) * lda + j0 + j] = D[e];
     }
 }
+// The three whole-matrix passes below walk rows per CTA and columns per thread (no index division), four
+// columns at a time where the rows are 16-byte aligned.
+__device__ __forceinline__ bool rows_are_vec4(const float* A, int64_t lda, int k) {
+    return (k & 3) == 0 && (lda & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0;
+}
+
 __global__ void zero_upper_kernel(float* A, int64_t lda, int k) {
-    const int64_t total = (int64_t)k * k;
-    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
-         e += (int64_t)gridDim.x * blockDim.x) {
-        const int i = (int)(e / k), j = (int)(e % k);
-        if (j > i) A[(int64_t)i * lda + j] = 0.0f;
+    for (int i = blockIdx.x; i < k; i += gridDim.x) {
+        float* row = A + (int64_t)i * lda;
+        for (int j = i + 1 + threadIdx.x; j < k; j += blockDim.x) row[j] = 0.0f;
     }
 }
 
 constexpr int RED_BLOCKS = 1024;
 __global__ void __launch_bounds__(256) abs_partial_kernel(const float* A, int64_t lda, int k, double* partial) {
     __shared__ double sh[256];
-    const int64_t total = (int64_t)k * k;
     double s = 0.0;
-    for (int64_t e = blockIdx.x * 256ll + threadIdx.x; e < total; e += (int64_t)RED_BLOCKS * 256)
-        s += fabs((double)A[(e / k) * lda + (e % k)]);
+    const bool vec = rows_are_vec4(A, lda, k);
+    for (int i = blockIdx.x; i < k; i += RED_BLOCKS) {   // fixed assignment of entries to threads: same sum every run
+        const float* row = A + (int64_t)i * lda;
+        if (vec) {
+            for (int j4 = threadIdx.x; j4 < (k >> 2); j4 += 256) {
+                const float4 v = *reinterpret_cast<const float4*>(row + 4 * j4);
+                s += (double)fabsf(v.x) + (double)fabsf(v.y) + (double)fabsf(v.z) + (double)fabsf(v.w);
+            }
+        } else {
+            for (int j = threadIdx.x; j < k; j += 256) s += (double)fabsf(row[j]);
+        }
+    }
     sh[threadIdx.x] = s;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
@@ -390,10 +403,19 @@ __global__ void __launch_bounds__(256) abs_final_kernel(const double* partial, i
 }
 __global__ void scale_by_inverse_kernel(float* A, int64_t lda, int k, const float* mean) {
     const float inv = 1.0f / *mean;
-    const int64_t total = (int64_t)k * k;
-    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
-         e += (int64_t)gridDim.x * blockDim.x)
-        A[(e / k) * lda + (e % k)] *= inv;
+    const bool vec = rows_are_vec4(A, lda, k);
+    for (int i = blockIdx.x; i < k; i += gridDim.x) {
+        float* row = A + (int64_t)i * lda;
+        if (vec) {
+            for (int j4 = threadIdx.x; j4 < (k >> 2); j4 += blockDim.x) {
+                float4 v = *reinterpret_cast<float4*>(row + 4 * j4);
+                v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+                *reinterpret_cast<float4*>(row + 4 * j4) = v;
+            }
+        } else {
+            for (int j = threadIdx.x; j < k; j += blockDim.x) row[j] *= inv;
+        }
+    }
 }
 
 struct InvLayout {
