@@ -585,8 +585,16 @@ __global__ void pack_kernel(const In* __restrict__ src, uint16_t* __restrict__ p
         rest = i >> 9;
         // consecutive CTAs take neighbouring pieces of the same source rows: along k when the operand
         // rows are source rows, along the operand rows when they are source columns
-        const uint32_t kb = TRANS ? (uint32_t)(rest / rowblocks) : (uint32_t)(rest % kblocks);
-        const uint64_t rb = TRANS ? rest % rowblocks : rest / kblocks;
+        uint32_t kb;
+        uint64_t rb;
+        if (rest <= 0xffffffffull) {  // 32-bit divisions whenever the piece number fits (it nearly always does)
+            const uint32_t r32 = (uint32_t)rest, d = TRANS ? rowblocks : kblocks, q = r32 / d, m = r32 - q * d;
+            kb = TRANS ? q : m;
+            rb = TRANS ? m : q;
+        } else {
+            kb = TRANS ? (uint32_t)(rest / rowblocks) : (uint32_t)(rest % kblocks);
+            rb = TRANS ? rest % rowblocks : rest / kblocks;
+        }
         const uint64_t R = rb * 128u + r, k0 = (uint64_t)kb * 32u + oct * 8u;
         uint16_t hi[8], lo[8];
         float up = 1.0f;
