@@ -696,6 +696,64 @@ def run_rows_sweep(lib, fast_jl, _lib, dev, D, rows_list=(16, 32, 64, 128, 256, 
     return out
 
 
+def run_stored_matrix(lib, fast_jl, _lib, dev, D, rows_list=(128, 256, 512)):
+    """The Gaussian projection of the C2 shape with the matrix kept in HBM (fast_jl.StoredMatrix: 91.6 GB for
+    D = 11,173,962, k = 4096) instead of regenerated in every call -- what a projector that serves many batches
+    with one seed can do on a 180 GB GPU.  Reports the one-off generation time and, per batch size, ms per call,
+    examples/s and the HBM rate of the matrix stream (a call of up to 256 rows reads the matrix once)."""
+    import torch
+    peak, _ = measured_peaks()
+    need = fast_jl.StoredMatrix.nbytes(D, K_DIM, TILES)
+    free, _ = torch.cuda.mem_get_info(dev)
+    if need + max(rows_list) * D * 6 > free:
+        return {"unavailable": f"needs {need / 1e9:.1f} GB for the matrix, {free / 1e9:.1f} GB free"}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    m = fast_jl.StoredMatrix(D, K_DIM, SEED, TILES, _lib.TB_NORMAL, dtype=torch.float16, device=dev)
+    ev1.record()
+    torch.cuda.synchronize()
+    gen_ms = ev0.elapsed_time(ev1)
+    gen = torch.Generator(device=dev).manual_seed(4321)
+    big = torch.empty(max(rows_list), D, device=dev, dtype=torch.float16)
+    for i in range(0, big.shape[0], 64):
+        big[i:i + 64] = (torch.randn(min(64, big.shape[0] - i), D, device=dev, generator=gen) * 1e-2).half()
+    res = {"matrix_bytes": need, "generation_ms": gen_ms, "rows": list(rows_list), "ms": [], "examples_per_s": [],
+           "frac_of_sustained_peak": [], "matrix_stream_tb_per_s": []}
+    for r in rows_list:
+        g = big[:r]
+        out = torch.empty(r, K_DIM, device=dev)
+        for _ in range(2):
+            fast_jl.project(g, K_DIM, SEED, TILES, _lib.TB_NORMAL, out=out, strict=False, matrix=m)
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fast_jl.project(g, K_DIM, SEED, TILES, _lib.TB_NORMAL, out=out, strict=False, matrix=m)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        t = statistics.median(times)
+        res["ms"].append(round(t, 3))
+        res["examples_per_s"].append(round(r / t * 1e3, 1))
+        res["frac_of_sustained_peak"].append(round(2.0 * r * D * K_DIM / (t * 1e-3) / 1e12 / peak, 4))
+        res["matrix_stream_tb_per_s"].append(round(need * -(-r // 256) / (t * 1e-3) / 1e12, 3))
+    # same result as the regenerating path (one-hot row and a random row of the 128-row batch)
+    chk = big[:128].clone()
+    chk[0].zero_()
+    chk[0, D // 3] = 1.0
+    a = fast_jl.project(chk, K_DIM, SEED, TILES, _lib.TB_NORMAL, strict=False, matrix=m)
+    b = fast_jl.project(chk, K_DIM, SEED, TILES, _lib.TB_NORMAL, strict=False)
+    res["one_hot_row_bit_equal"] = bool(torch.equal(a[0], b[0]))
+    res["max_row_relative_difference"] = float(((a - b).norm(dim=1) / b.norm(dim=1)).max())
+    _lib.device_status(dev.index)
+    del m, big, a, b, chk
+    fast_jl.free_workspaces()
+    torch.cuda.empty_cache()
+    res["what"] = ("Gaussian matrix of the benchmark shape generated once and kept in HBM; every call reads it "
+                   "(once per 256 rows) instead of regenerating it")
+    return res
+
+
 def run_scaling_strong(lib, fast_jl, _lib, g, rank, world):
     """The 128-row batch of the configuration split over the ranks (128 / N rows each, same virtual matrix, no
     collective): examples/s = 128 / (slowest rank's time per call)."""
@@ -1021,6 +1079,13 @@ def run_ours(args, D):
             sweep = run_rows_sweep(lib, fast_jl, _lib, dev, D)
         except Exception as e:  # an extra measurement must not take the main line down
             sweep = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    stored = None
+    if extras and rank == 0:
+        try:
+            stored = run_stored_matrix(lib, fast_jl, _lib, dev, D)
+        except Exception as e:
+            stored = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
     scoring = None if args.no_scoring else run_scoring(args, dev, rank, world, args.scale)
@@ -1085,6 +1150,8 @@ def run_ours(args, D):
             line["rows_sweep"] = sweep
         if strong is not None:
             line["scaling_strong"] = strong
+        if stored is not None:
+            line["stored_matrix"] = stored
         line["strict"] = ("timed with strict=False (no device synchronisation after each call); the drop-in default "
                           "TRAK_B200_STRICT=1 adds a cudaDeviceSynchronize and a status read per call")
         if featurize is not None:

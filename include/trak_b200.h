@@ -121,6 +121,40 @@ int tb_project_segments(int device, void *stream, const tb_segment *segs, int32_
                         uint32_t num_feature_tiles, int proj_type, float alpha, int accumulate,
                         void *ws, size_t ws_bytes);
 
+/* ---- projection with a stored matrix -----------------------------------------------
+ * No counterpart in the reference, which regenerates its matrix in every call because D x k
+ * entries do not fit the GPUs it was written for.  On a B200 they can: the matrix of
+ * (F, N, seed, num_feature_tiles, proj_type) takes tb_matrix_bytes(...) bytes (2 bytes per
+ * entry, feature tiles padded to 64 features: 91.6 GB for F = 11,173,962, N = 4096), and
+ * reading it from HBM is about three times faster than regenerating a Gaussian matrix.
+ * For a projector that serves many batches with one seed (TRAKer.featurize over a train
+ * set):
+ *
+ *   tb_matrix_generate  fills `matrix` (device memory of the caller, 256-byte aligned, at
+ *                       least tb_matrix_bytes) with the very entries tb_project generates,
+ *                       as 16-bit values of `elem_dtype`: TB_F16 for fp16 and fp32
+ *                       gradients, TB_BF16 for bf16 gradients
+ *   tb_project_cached   out = alpha * grads . P (+ out) with P read from `matrix`; same
+ *                       arguments, workspace and result as tb_project (seed and proj_type
+ *                       are properties of the stored matrix); rows are walked 256 at a
+ *                       time, each pass reading the matrix once
+ *
+ * The Rademacher matrix is cheaper to regenerate than to read at 128 rows and more; the
+ * stored form pays for the Gaussian matrix and for small Rademacher batches. */
+size_t tb_matrix_bytes(int64_t F, uint32_t N, uint32_t num_feature_tiles);
+int tb_matrix_generate(int device, void *stream, int64_t F, uint32_t N, uint32_t seed,
+                       uint32_t num_feature_tiles, int proj_type, int elem_dtype, void *matrix,
+                       size_t matrix_bytes);
+int tb_project_cached(int device, void *stream, const void *grads, int dtype, int64_t B, int64_t F,
+                      int64_t ld, float *out, int64_t ld_out, uint32_t N, uint32_t num_feature_tiles,
+                      const void *matrix, size_t matrix_bytes, float alpha, int accumulate, void *ws,
+                      size_t ws_bytes);
+/* The same from the per-parameter gradient tensors (the table of tb_project_segments above). */
+int tb_project_segments_cached(int device, void *stream, const tb_segment *segs, int32_t nsegs,
+                               int dtype, int64_t B, float *out, int64_t ld_out, uint32_t N,
+                               uint32_t num_feature_tiles, const void *matrix, size_t matrix_bytes,
+                               float alpha, int accumulate, void *ws, size_t ws_bytes);
+
 /* ---- after-kernel scoring -------------------------------------------------------
  * The three products and the inverse of the reference's BasicScoreComputer
  * (trak/score_computers.py:114-189).  Matrices are row-major; `dtype` is the type of

@@ -339,10 +339,22 @@ def test_full_benchmark_shape_all_rows_against_the_reference_kernel(cuda):
     for i, f in enumerate(feats):
         g[i].zero_()
         g[i, f] = 1.0
+    rows, groups = [8, 9, 64, 127], [0, 77]
+    cols = np.concatenate([np.arange(32 * c, 32 * c + 32) for c in groups])
+    g_rows = g[rows].cpu().numpy()
     for name, p in (("rademacher", RAD), ("normal", NOR)):
         got = ours(g, N, seed, T, p)
         ref = getattr(w, f"project_{name}_32")(g, N, seed, T)
         assert torch.equal(got[:len(feats)], ref[:len(feats)]), name
+        # four random rows on 64 columns against the fp64 product with the identical matrix: what the long
+        # tensor-core accumulations (302,000 features per CTA, truncating fp32 adds) cost at this size
+        exact = o.project_column_groups(p, g_rows, seed, T, groups)
+        mine = got[rows][:, cols].double().cpu().numpy()
+        theirs = ref[rows][:, cols].double().cpu().numpy()
+        e_mine = (np.linalg.norm(mine - exact, axis=1) / np.linalg.norm(exact, axis=1)).max()
+        e_ref = (np.linalg.norm(theirs - exact, axis=1) / np.linalg.norm(exact, axis=1)).max()
+        print(f"{name}: against the fp64 oracle on 64 columns: this library {e_mine:.2e}, reference kernel {e_ref:.2e}")
+        assert e_mine <= TOL, (name, e_mine)
         err = ((got - ref).double().norm(dim=1) / ref.double().norm(dim=1))[len(feats):].max().item()
         print(f"{name}: 120 random rows against the reference kernel, worst row {err:.2e}")
         assert err <= TOL, (name, err)
@@ -440,6 +452,65 @@ def test_wide_gaussian_from_segments(cuda):
     flat = torch.cat([t.reshape(B, 1) if t.dim() < 2 else t.flatten(start_dim=1) for t in tensors], dim=1)
     a = fast_jl.project_segments(tensors, 1024, 21, 148, NOR)
     assert torch.equal(a, fast_jl.project(flat.contiguous(), 1024, 21, 148, NOR))
+
+
+STORED_SHAPES = [  # B, F, N, seed, tiles, dtype
+    (16, 20011, 1024, 17, 148, "f16"),
+    (130, 9473, 512, 5, 7, "f32"),
+    (300, 4097, 512, 99, 37, "bf16"),     # two passes of the stored-matrix kernel
+    (5, 16, 512, 9, 148, "f16"),          # fewer features than tiles
+    (64, 4096, 1536, 4, 4, "f16"),        # tile size a multiple of 64
+]
+
+
+@pytest.mark.parametrize("p", [RAD, NOR])
+@pytest.mark.parametrize("B,F,N,seed,T,dt", STORED_SHAPES)
+def test_stored_matrix_projection(cuda, p, B, F, N, seed, T, dt):
+    """The matrix materialised once in device memory and read back by a plain two-operand GEMM: one-hot rows
+    must give the very bits of the on-the-fly generator, random rows agree to fp32 summation order and with the
+    fp64 oracle."""
+    from trak_b200 import fast_jl
+    g_cpu = (torch.randn(B, F, generator=torch.Generator().manual_seed(B + F)) * 0.1).to(DT[dt])
+    fts = o.feature_tile_size(F, T)
+    feats = sorted({0, min(F - 1, 15), min(F - 1, 16), min(F - 1, fts - 1), min(F - 1, fts), F - 1})[:B]
+    for r, f in enumerate(feats):
+        g_cpu[r].zero_()
+        g_cpu[r, f] = 1.0
+    g = g_cpu.to(cuda)
+    m = fast_jl.StoredMatrix(F, N, seed, T, p, dtype=DT[dt], device=cuda)
+    assert m.data.numel() == fast_jl.StoredMatrix.nbytes(F, N, T) >= 2 * F * N
+    stored = ours(g, N, seed, T, p, matrix=m)
+    fly = ours(g, N, seed, T, p)
+    assert torch.equal(stored[:len(feats)], fly[:len(feats)])
+    assert rel_rows(stored.cpu().numpy(), fly.cpu().numpy()) <= 1e-4
+    assert torch.equal(stored, ours(g, N, seed, T, p, matrix=m))          # run-to-run identical
+    if dt != "bf16" or p == RAD:
+        ref = o.project(p, as_numpy_input(g_cpu), N, seed, T, round_f16=(dt == "f32"))
+        assert rel_rows(stored.cpu().numpy(), ref) <= TOL
+    out = torch.full((B, N), 0.5, device=cuda)
+    ours(g, N, seed, T, p, matrix=m, alpha=0.25, out=out, accumulate=True)
+    torch.testing.assert_close(out, 0.5 + 0.25 * stored, rtol=1e-6, atol=1e-5)
+    with pytest.raises(RuntimeError):
+        ours(g, N, seed + 1, T, p, matrix=m)      # a matrix of another seed is refused
+
+
+def test_stored_matrix_through_the_projector_and_from_segments(cuda):
+    from trak_b200 import fast_jl
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    B = 40
+    shapes = [(64, 3, 3, 3), (), (17,), (129, 31), (300, 7, 2)]
+    grads = {i: torch.randn((B,) + sh, device=cuda) for i, sh in enumerate(shapes)}
+    D = sum(int(np.prod(sh)) if len(sh) else 1 for sh in shapes)
+    plain = CudaProjector(D, 1024, 3, ProjectionType.normal, cuda, 32)
+    keep = CudaProjector(D, 1024, 3, ProjectionType.normal, cuda, 32, store_matrix=True)
+    for model_id in (0, 1, 0):                      # a new model_id means a new seed: the matrix is replaced
+        a, b = plain.project(grads, model_id), keep.project(grads, model_id)
+        assert rel_rows(b.cpu().numpy(), a.cpu().numpy()) <= 1e-4
+        assert keep._matrix is not None and keep._matrix.seed == 3 + 10_000 * model_id
+    flat = torch.cat([t.reshape(B, 1) if t.dim() < 2 else t.flatten(start_dim=1) for t in grads.values()], dim=1)
+    assert torch.equal(keep.project(grads, 0), keep.project(flat.contiguous(), 0))   # segments == dense
+    keep.free_memory()
+    assert keep._matrix is None
 
 
 def test_bounded_wait_times_out_and_device_stays_usable(cuda):

@@ -49,6 +49,11 @@ SIGNATURES = {
     "tb_spd_inverse": (_i, [_i, _vp, _vp, _i64, _i64, _f, _i, _vp, _vp, _sz]),
     "tb_gemm_nt_workspace_bytes": (_sz, [_i, _i64, _i64, _i64]),
     "tb_gemm_nt": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i, _i64, _i64, _i64, _vp, _i64, _vp, _f, _i, _vp, _sz]),
+    "tb_matrix_bytes": (_sz, [_i64, _u32, _u32]),
+    "tb_matrix_generate": (_i, [_i, _vp, _i64, _u32, _u32, _u32, _i, _i, _vp, _sz]),
+    "tb_project_cached": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _vp, _sz, _f, _i, _vp, _sz]),
+    "tb_project_segments_cached": (_i, [_i, _vp, ctypes.POINTER(Segment), _i32, _i, _i64, _vp, _i64, _u32, _u32, _vp,
+                                        _sz, _f, _i, _vp, _sz]),
     "tb_finalize_scores": (_i, [_i, _vp, _vp, _i64, _vp, _i64, _i64, _f, _vp, _i, _i64]),
     "tb_project_static": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i]),
     "tb_project": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i64, _vp, _i64, _u32, _u32, _u32, _i, _f, _i,

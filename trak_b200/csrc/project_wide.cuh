@@ -40,6 +40,7 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
     __shared__ uint64_t bar_full_b[WIDE_MAX_STAGES];
     __shared__ uint64_t bar_empty_b[WIDE_MAX_STAGES];
     __shared__ uint64_t bar_acc;
+    __shared__ uint64_t bar_drained;
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_word;
     volatile uint32_t* abort_flag = &abort_word;
@@ -70,6 +71,7 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
             mbar_init(smem_u32(&bar_empty_b[s]), 1);
         }
         mbar_init(smem_u32(&bar_acc), 1);
+        mbar_init(smem_u32(&bar_drained), 4u * NG * 32u);
         abort_word = 0;
         fence_mbar_init();
     }
@@ -98,58 +100,52 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
             const uint32_t by = tile0 + ti;
             Xw st;
             xw_seed(st, p.seed + 658105236u * stream_col + 359124577u * by);
-            for (uint32_t s = 0; s < p.nst; ++s) {
-                bool got = mbar_wait(smem_u32(&bar_empty_a[g][slot]), ph ^ 1u, abort_flag);
-                got = __all_sync(0xffffffffu, got);
-                if (!got) {
-                    if (lane == 0) fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, (g << 16) | s);
-                    ok = false;
-                    break;
-                }
-                const uint32_t dst = row_addr + slot * WIDE_A_BYTES;
-                // one copy of the (long) Gaussian chunk body keeps the loop in the instruction cache
-                constexpr int CHUNK_UNROLL = PTYPE == TB_NORMAL ? 1 : 2;
+            // a chain of the accumulators ends every p.epoch stages and at the end of the tile
+            for (uint32_t s0 = 0; s0 < p.nst && ok; s0 += p.epoch) {
+                const uint32_t s1 = min(s0 + p.epoch, p.nst);
+                for (uint32_t s = s0; s < s1; ++s) {
+                    bool got = mbar_wait(smem_u32(&bar_empty_a[g][slot]), ph ^ 1u, abort_flag);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) {
+                        if (lane == 0) fail(p.status, abort_flag, ST_TIMEOUT_EMPTY, (g << 16) | s);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = row_addr + slot * WIDE_A_BYTES;
+                    // one copy of the (long) Gaussian chunk body keeps the loop in the instruction cache
+                    constexpr int CHUNK_UNROLL = PTYPE == TB_NORMAL ? 1 : 2;
 #pragma unroll CHUNK_UNROLL
-                for (uint32_t c = 0; c < 2; ++c) {
-                    uint32_t w[8];
-                    if (PTYPE == TB_RADEMACHER)
-                        gen_rademacher<BF16>(st, h, w);
-                    else
-                        gen_normal<BF16>(st, h, sel_lo, sel_hi, w);
-                    // features 16c .. 16c+15 of this column: 16-byte pieces 2c and 2c + 1 of the row
-                    st_shared_v4(dst + (((2u * c) ^ sw) << 4), w[0], w[1], w[2], w[3]);
-                    st_shared_v4(dst + (((2u * c + 1u) ^ sw) << 4), w[4], w[5], w[6], w[7]);
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&bar_full_a[g][slot]));
-                if (++slot == SA) {
-                    slot = 0;
-                    ph ^= 1u;
-                }
-            }
-        }
-        if (ok) {
-            bool got = mbar_wait(smem_u32(&bar_acc), 0u, abort_flag);
-            got = __all_sync(0xffffffffu, got);
-            if (!got) {
-                if (lane == 0) fail(p.status, abort_flag, ST_TIMEOUT_ACC, g);
-            } else {
-                tc_fence_after();
-                // TMEM lane m holds output column n_out; TMEM column b holds batch row b
-                const uint32_t n_out = col0 + q * 32u + 2u * (lane & 15u) + h;
-                float* dst = p.partials + (size_t)blockIdx.y * p.B * p.N + n_out;
-                const uint32_t lane_base = (q * 32u) << 16;
-                for (uint32_t cb = g; cb < p.Bpad / 16u; cb += NG) {
-                    uint32_t r[16];
-                    tmem_ld_x16(tmem_base + lane_base + cb * 16u, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const uint32_t b = cb * 16u + j;
-                        if (b < p.B) dst[(size_t)b * p.N] = __uint_as_float(r[j]);
+                    for (uint32_t c = 0; c < 2; ++c) {
+                        uint32_t w[8];
+                        if (PTYPE == TB_RADEMACHER)
+                            gen_rademacher<BF16>(st, h, w);
+                        else
+                            gen_normal<BF16>(st, h, sel_lo, sel_hi, w);
+                        // features 16c .. 16c+15 of this column: 16-byte pieces 2c and 2c + 1 of the row
+                        st_shared_v4(dst + (((2u * c) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+                        st_shared_v4(dst + (((2u * c + 1u) ^ sw) << 4), w[4], w[5], w[6], w[7]);
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(smem_u32(&bar_full_a[g][slot]));
+                    if (++slot == SA) {
+                        slot = 0;
+                        ph ^= 1u;
                     }
                 }
+                if (!ok) break;
+                const uint32_t tl = (ti - g) / NG;  // tiles this group has finished
+                ok = drain_accumulators<NG, 4u>(p, smem_u32(&bar_acc), smem_u32(&bar_drained), &tmem_slot,
+                                                tl * p.drains_per_tile + s0 / p.epoch,
+                                                !(s1 == p.nst && tl + 1u == (ntile + NG - 1) / NG), abort_flag);
             }
+        }
+        // the drains of the tiles that group 0 still runs after this group's tiles are done
+        {
+            const uint32_t drains = ((ntile + NG - 1) / NG) * p.drains_per_tile;
+            uint32_t d = (ntile > g ? (ntile - g + NG - 1) / NG : 0u) * p.drains_per_tile;
+            for (; ok && d < drains; ++d)
+                ok = drain_accumulators<NG, 4u>(p, smem_u32(&bar_acc), smem_u32(&bar_drained), &tmem_slot, d,
+                                                d + 1u < drains, abort_flag);
         }
     } else {
         // blocks (32 features x 128 columns x all rows) each group contributes
@@ -197,7 +193,8 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
             // whole warp in the loop, one elected lane issues (operands stay in uniform registers)
             const bool leader = elect_one();
             bool ok = true;
-            uint32_t started = 0;
+            uint32_t started = 0, epoch_no = 0;
+            uint32_t chain_end = min(p.epoch, p.nst);  // stages of every group until the current chain ends
             uint32_t aslot = 0, aph = 0, bslot = 0, bph = 0;
             for (uint32_t it = 0; it < maxcnt && ok; ++it) {
 #pragma unroll
@@ -240,6 +237,21 @@ project_wide_kernel(const __grid_constant__ CUtensorMap tmap, const ProjParams p
                 if (++aslot == SA) {
                     aslot = 0;
                     aph ^= 1u;
+                }
+                if (it + 1 == chain_end && ok && it + 1 < maxcnt) {
+                    // end of an accumulation chain (every p.epoch stages of a feature tile and at its end): hand the
+                    // accumulators to the generator warps, start afresh
+                    chain_end += min(p.epoch, p.nst - chain_end % p.nst);
+                    if (leader) tc_commit(smem_u32(&bar_acc));
+                    const bool got = mbar_wait(smem_u32(&bar_drained), epoch_no & 1u, abort_flag);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        if (leader) fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x8000u | it);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    started = 0;
+                    ++epoch_no;
                 }
             }
             if (ok && leader) tc_commit(smem_u32(&bar_acc));

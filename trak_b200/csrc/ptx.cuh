@@ -154,6 +154,20 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 
+// One warp reads 8 consecutive 32-bit columns of its own 32 lanes.
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Fire-and-forget fp32 add (round to nearest) performed by the L2: no read comes back to the SM.
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
 // ---- MMA issue ----------------------------------------------------------------
 // D[tmem] (+)= A[tmem] * B[smem descriptor], kind::f16 (fp16 or bf16 operands,
 // fp32 accumulate).  Issued by exactly one thread.

@@ -51,8 +51,45 @@ def free_workspaces():
     _workspaces.clear()
 
 
+class StoredMatrix:
+    """The projection matrix of ``(F, N, seed, num_feature_tiles, proj_type)`` materialised in device memory
+    (``2 * N`` bytes per feature: 91.6 GB for F = 11,173,962 and N = 4096), for ``project(..., matrix=...)``.
+    ``dtype`` is the gradients' dtype it will be used with (fp32 gradients are rounded to fp16 on the way in,
+    so they take the fp16 form).  Entries are bit for bit what ``project`` generates on the fly."""
+
+    def __init__(self, F, N, seed, num_feature_tiles, proj_type, dtype=torch.float16, device="cuda"):
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("StoredMatrix needs a CUDA device")
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.F, self.N = int(F), _u32("N", N)
+        self.seed, self.tiles = _u32("seed", seed), _u32("num_feature_tiles", num_feature_tiles)
+        self.proj_type, self.device = int(proj_type), dev
+        self.elem = _lib.TB_BF16 if dtype == torch.bfloat16 else _lib.TB_F16
+        l = _lib.lib()
+        nbytes = l.tb_matrix_bytes(self.F, self.N, max(self.tiles, 1))
+        if nbytes == 0:
+            _lib.check(_lib.TB_ERR_BAD_PROJ_DIM if self.N % 512 else 2)
+        self.data = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            _lib.check(l.tb_matrix_generate(dev.index, stream, self.F, self.N, self.seed, self.tiles, self.proj_type,
+                                            self.elem, self.data.data_ptr(), nbytes))
+            _lib.device_status(dev.index)
+
+    @staticmethod
+    def nbytes(F, N, num_feature_tiles):
+        return _lib.lib().tb_matrix_bytes(int(F), int(N), int(num_feature_tiles))
+
+    def matches(self, input, N, num_feature_tiles):
+        elem = _lib.TB_BF16 if input.dtype == torch.bfloat16 else _lib.TB_F16
+        return input.shape[1] == self.F and N == self.N and num_feature_tiles == self.tiles and \
+            elem == self.elem and input.device == self.device
+
+
 def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None, accumulate=False,
-            strict=None, allow_strided=False):
+            strict=None, allow_strided=False, matrix=None):
     """``alpha * input @ P`` with the fast_jl matrix P(seed, num_feature_tiles, proj_type).
 
     ``out`` (float32 [B, N], rows 16-byte aligned) and ``accumulate`` let callers
@@ -61,7 +98,9 @@ def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None
     the kernels and raises if one of them gave up a bounded wait.  With
     ``allow_strided`` the rows may be further apart than their length (a column
     slice of a wider buffer); the six ``project_*`` entry points keep the
-    reference's contiguity check.
+    reference's contiguity check.  With ``matrix`` (a ``StoredMatrix`` made for the
+    same shape, seed, tile count, type and 16-bit gradient format) the matrix is
+    read from device memory instead of being regenerated.
     """
     if not isinstance(input, torch.Tensor) or not input.is_cuda:
         raise RuntimeError("input must be a CUDA tensor")
@@ -92,10 +131,18 @@ def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None
         stream = torch.cuda.current_stream(dev).cuda_stream
         nbytes = l.tb_project_workspace_bytes(dt, B, F, N, max(num_feature_tiles, 1))
         ws = _workspace(dev, stream, max(nbytes, 256))
-        rc = l.tb_project(dev.index, stream, input.data_ptr(), dt, B, F, input.stride(0),
-                          out.data_ptr(), out.stride(0), N, seed, num_feature_tiles,
-                          int(proj_type), float(alpha), int(bool(accumulate)), ws.data_ptr(),
-                          ws.numel())
+        if matrix is not None:
+            if not matrix.matches(input, N, num_feature_tiles) or matrix.seed != seed or \
+                    matrix.proj_type != int(proj_type):
+                raise RuntimeError("the stored matrix was made for another shape, seed, type or gradient dtype")
+            rc = l.tb_project_cached(dev.index, stream, input.data_ptr(), dt, B, F, input.stride(0), out.data_ptr(),
+                                     out.stride(0), N, num_feature_tiles, matrix.data.data_ptr(), matrix.data.numel(),
+                                     float(alpha), int(bool(accumulate)), ws.data_ptr(), ws.numel())
+        else:
+            rc = l.tb_project(dev.index, stream, input.data_ptr(), dt, B, F, input.stride(0),
+                              out.data_ptr(), out.stride(0), N, seed, num_feature_tiles,
+                              int(proj_type), float(alpha), int(bool(accumulate)), ws.data_ptr(),
+                              ws.numel())
         _lib.check(rc)
         if _STRICT if strict is None else strict:
             _lib.device_status(dev.index)
@@ -103,7 +150,7 @@ def project(input, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None
 
 
 def project_segments(tensors, N, seed, num_feature_tiles, proj_type, *, alpha=1.0, out=None, accumulate=False,
-                     strict=None):
+                     strict=None, matrix=None):
     """Projects the per-sample gradient whose sample b is the concatenation of ``t[b].reshape(-1)`` over
     ``tensors`` (a list of CUDA tensors ``[B, *shape]``, one dtype, each with contiguous samples) without
     first copying them into one ``[B, D]`` matrix.  A tensor with fewer than two dimensions contributes one
@@ -145,9 +192,18 @@ def project_segments(tensors, N, seed, num_feature_tiles, proj_type, *, alpha=1.
         stream = torch.cuda.current_stream(dev).cuda_stream
         nbytes = l.tb_project_segments_workspace_bytes(dt, B, F, N, max(num_feature_tiles, 1), len(tensors))
         ws = _workspace(dev, stream, max(nbytes, 256))
-        rc = l.tb_project_segments(dev.index, stream, segs, len(tensors), dt, B, out.data_ptr(), out.stride(0), N,
-                                   seed, num_feature_tiles, int(proj_type), float(alpha), int(bool(accumulate)),
-                                   ws.data_ptr(), ws.numel())
+        if matrix is not None:
+            elem = _lib.TB_BF16 if dtype == torch.bfloat16 else _lib.TB_F16
+            if (matrix.F, matrix.N, matrix.tiles, matrix.elem, matrix.device) != (F, N, num_feature_tiles, elem, dev) \
+                    or matrix.seed != seed or matrix.proj_type != int(proj_type):
+                raise RuntimeError("the stored matrix was made for another shape, seed, type or gradient dtype")
+            rc = l.tb_project_segments_cached(dev.index, stream, segs, len(tensors), dt, B, out.data_ptr(), out.stride(0),
+                                              N, num_feature_tiles, matrix.data.data_ptr(), matrix.data.numel(),
+                                              float(alpha), int(bool(accumulate)), ws.data_ptr(), ws.numel())
+        else:
+            rc = l.tb_project_segments(dev.index, stream, segs, len(tensors), dt, B, out.data_ptr(), out.stride(0), N,
+                                       seed, num_feature_tiles, int(proj_type), float(alpha), int(bool(accumulate)),
+                                       ws.data_ptr(), ws.numel())
         _lib.check(rc)
         if _STRICT if strict is None else strict:
             _lib.device_status(dev.index)
