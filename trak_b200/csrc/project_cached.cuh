@@ -52,15 +52,17 @@ __global__ void __launch_bounds__(128) materialize_kernel(uint16_t* __restrict__
 
 // One CTA = 128 output columns x up to 256 rows x a bundle of feature tiles.  Warp 0 issues TMA (a stored matrix
 // tile and the matching gradient box per 64 features, never multicast), warp 1 the MMAs, warps 2-5 read the
-// accumulator out.  Both operands come from shared memory; the kernel is bound by the HBM stream of the matrix.
+// accumulators out.  Both operands come from shared memory; the kernel is bound by the HBM stream of the matrix.
+// The accumulation chains (ProjParams::epoch) alternate between two accumulators of 256 TMEM columns, so the MMA
+// warp starts the next chain while the epilogue warps add the finished one to the partial.
 __global__ void __launch_bounds__(192, 1)
 project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const ProjParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[CACHED_MAX_STAGES];
     __shared__ uint64_t bar_empty[CACHED_MAX_STAGES];
-    __shared__ uint64_t bar_acc;
-    __shared__ uint64_t bar_drained;
+    __shared__ uint64_t bar_acc[2];
+    __shared__ uint64_t bar_drained[2];
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_word;
     volatile uint32_t* abort_flag = &abort_word;
@@ -79,13 +81,15 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
-        mbar_init(smem_u32(&bar_acc), 1);
-        mbar_init(smem_u32(&bar_drained), 128u);
+        for (uint32_t a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bar_acc[a]), 1);
+            mbar_init(smem_u32(&bar_drained[a]), 128u);
+        }
         abort_word = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(&tmem_slot), 256u);
+        tmem_alloc(smem_u32(&tmem_slot), 512u);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -139,7 +143,8 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (leader) {
 #pragma unroll
                 for (uint32_t k = 0; k < 4; ++k)  // 16 features further: 32 bytes inside the swizzle row
-                    umma_f16_ss(tmem_base, a_desc + 2u * k, b_desc + 2u * k, p.idesc, started | (k > 0 ? 1u : 0u));
+                    umma_f16_ss(tmem_base + (epoch_no & 1u) * 256u, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                                started | (k > 0 ? 1u : 0u));
                 tc_commit(smem_u32(&bar_empty[slot]));
             }
             started = 1u;
@@ -148,21 +153,24 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 ph ^= 1u;
             }
             if (--until == 0 && it + 1 < nblocks) {
-                // end of an accumulation chain (see ProjParams::epoch): drain, then start from zero
+                // end of an accumulation chain (see ProjParams::epoch): hand this accumulator to the epilogue warps
+                // and go on in the other one, once its chain before last has been read out
                 until = p.epoch;
-                if (leader) tc_commit(smem_u32(&bar_acc));
-                got = mbar_wait(smem_u32(&bar_drained), epoch_no & 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) {
-                    if (leader) fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x8000u | it);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
+                if (leader) tc_commit(smem_u32(&bar_acc[epoch_no & 1u]));
                 started = 0;
                 ++epoch_no;
+                if (epoch_no >= 2u) {
+                    got = mbar_wait(smem_u32(&bar_drained[epoch_no & 1u]), ((epoch_no >> 1) - 1u) & 1u, abort_flag);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        if (leader) fail(p.status, abort_flag, ST_TIMEOUT_ACC, 0x8000u | it);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                }
             }
         }
-        if (ok && leader) tc_commit(smem_u32(&bar_acc));
+        if (ok && leader) tc_commit(smem_u32(&bar_acc[epoch_no & 1u]));
     } else {
         // --------------------------------- epilogue ---------------------------------
         const uint32_t q = warp & 3u, h = lane >> 4;   // a warp reaches the TMEM lanes 32 (warp % 4) ...
@@ -171,7 +179,7 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const uint32_t lane_base = (q * 32u) << 16;
         const uint32_t drains = (nblocks + p.epoch - 1u) / p.epoch;
         for (uint32_t e = 0; e < drains; ++e) {
-            bool got = mbar_wait(smem_u32(&bar_acc), e & 1u, abort_flag);
+            bool got = mbar_wait(smem_u32(&bar_acc[e & 1u]), (e >> 1) & 1u, abort_flag);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
                 if (lane == 0) fail(p.status, abort_flag, ST_TIMEOUT_ACC, warp);
@@ -181,7 +189,7 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             // chain 0 stores, the later chains add in the L2 (see drain_accumulators)
             for (uint32_t cb = 0; cb < p.Bpad / 8u; ++cb) {
                 uint32_t r[8];
-                tmem_ld_x8(tmem_base + lane_base + cb * 8u, r);
+                tmem_ld_x8(tmem_base + lane_base + (e & 1u) * 256u + cb * 8u, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -194,9 +202,9 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     }
                 }
             }
-            if (e + 1 < drains) {
+            if (e + 2 < drains) {  // the chain after next accumulates here again
                 tc_fence_before();
-                mbar_arrive(smem_u32(&bar_drained));
+                mbar_arrive(smem_u32(&bar_drained[e & 1u]));
             }
         }
     }
@@ -206,7 +214,7 @@ project_cached_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (*abort_flag) __nanosleep(200000);  // let copies and MMAs already in flight land
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 256u);
+        tmem_dealloc(tmem_base, 512u);
     }
 }
 
