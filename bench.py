@@ -1080,7 +1080,7 @@ def run_ours(args, D):
         except Exception as e:  # an extra measurement must not take the main line down
             sweep = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     stored = None
-    if extras and rank == 0:
+    if extras and world == 1:
         try:
             stored = run_stored_matrix(lib, fast_jl, _lib, dev, D)
         except Exception as e:
