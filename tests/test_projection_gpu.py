@@ -454,6 +454,53 @@ def test_wide_gaussian_from_segments(cuda):
     assert torch.equal(a, fast_jl.project(flat.contiguous(), 1024, 21, 148, NOR))
 
 
+CHAIN_SHAPES = [  # B, F, tiles: feature tiles long enough for several accumulation chains per tile
+    (128, 98_304, 3),     # 32,768 features per tile: a whole number of chains for every kernel shape; NG > tiles
+    (128, 200_003, 5),    # ragged last chain; more tiles than generator groups of the 128-row shapes
+    (8, 150_001, 2),      # small batch: the generator-bound shape for both matrix types
+    (256, 120_007, 3),    # the 256-row shapes
+    (300, 98_304, 3),     # Gaussian: the 512-row kernel (32-feature stages), then nothing left
+    (300, 131_075, 9),    # Gaussian: 512-row kernel with more tiles than its seven groups
+]
+
+
+@pytest.mark.parametrize("p", [RAD, NOR])
+@pytest.mark.parametrize("B,F,T", CHAIN_SHAPES)
+def test_accumulation_chains(cuda, p, B, F, T):
+    """The accumulators are read out and restarted every 2048 / 4096 MMA steps of a feature tile and at its end.
+    Feature tiles of 15,000 to 75,000 features make every kernel shape run several chains per tile, with chain ends
+    that do and do not coincide with the tile's end, with generator groups that have no tile at all, and with
+    groups that finish before the others: results against the fp64 oracle on four 32-column groups, one-hot rows
+    bit for bit against the oracle's matrix, the stored-matrix kernel against the regenerating one."""
+    from trak_b200 import fast_jl
+    N, seed = 1024, 29
+    g_cpu = (torch.randn(B, F, generator=torch.Generator().manual_seed(B + F + T)) * 0.1).half()
+    fts = o.feature_tile_size(F, T)
+    feats = [0, fts - 1, fts, F // 2, F - 1][:B]
+    for r, f in enumerate(feats):
+        g_cpu[r].zero_()
+        g_cpu[r, f] = 1.0
+    g = g_cpu.to(cuda)
+    out = ours(g, N, seed, T, p)
+    assert torch.equal(out, ours(g, N, seed, T, p))                      # run-to-run identical
+    groups = [0, 7, 16, 31]
+    cols = np.concatenate([np.arange(32 * c, 32 * c + 32) for c in groups])
+    ref = o.project_column_groups(p, g_cpu.numpy(), seed, T, groups)
+    got = out.cpu().numpy()[:, cols]
+    # one-hot rows are single matrix entries: exact whatever the number of chains (the oracle's Gaussian entries
+    # come from the host's libm, so that matrix is compared through a small batch of the same rows instead)
+    if p == RAD:
+        assert np.array_equal(out.cpu().numpy()[:len(feats)], o.matrix_rows(p, F, N, seed, T, feats))
+    else:
+        assert torch.equal(out[:len(feats)], ours(g[:len(feats)].contiguous(), N, seed, T, p))
+    err = rel_rows(got[len(feats):], ref[len(feats):])
+    assert err <= 1e-4, err      # short chains: well inside the 1e-3 tolerance of the projection
+    m = fast_jl.StoredMatrix(F, N, seed, T, p, dtype=torch.float16, device=cuda)
+    stored = ours(g, N, seed, T, p, matrix=m)
+    assert torch.equal(stored[:len(feats)], out[:len(feats)])
+    assert rel_rows(stored.cpu().numpy()[:, cols][len(feats):], ref[len(feats):]) <= 1e-4
+
+
 STORED_SHAPES = [  # B, F, N, seed, tiles, dtype
     (16, 20011, 1024, 17, 148, "f16"),
     (130, 9473, 512, 5, 7, "f32"),
