@@ -120,7 +120,7 @@ class CudaProjector:
         elem = _lib.TB_BF16 if dtype == torch.bfloat16 else _lib.TB_F16
         m = self._matrix
         if m is None or (m.seed, m.F, m.elem) != (seed, width, elem):
-            self._matrix = None   # release the old one before the new one is allocated
+            self._matrix = m = None   # drop every reference to the old one before the new one is allocated
             self._matrix = m = _fast_jl.StoredMatrix(width, self.proj_dim, seed, self.num_sms, self._ptype,
                                                      dtype=dtype, device=self.device)
         return m
