@@ -560,6 +560,47 @@ def test_stored_matrix_through_the_projector_and_from_segments(cuda):
     assert keep._matrix is None
 
 
+def test_stored_matrix_mode_of_the_entry_points(cuda, monkeypatch):
+    """``store_matrices(True)`` (env TRAK_B200_STORE_MATRIX=1): the six-function interface the reference's own
+    CudaProjector calls keeps the Gaussian matrix of the current (shape, seed) on the device.  Same results, one
+    matrix per device, replaced when the seed changes, never used for the Rademacher matrix, skipped when it does
+    not fit, argument errors unchanged."""
+    from trak_b200 import fast_jl
+    F, N, T = 20011, 1024, 148
+    g = (torch.randn(40, F, generator=torch.Generator().manual_seed(3)) * 0.1).half()
+    g[0].zero_()
+    g[0, 777] = 1.0
+    g = g.to(cuda)
+    plain = fast_jl.project_normal_32(g, N, 5, T)
+    fast_jl.store_matrices(True)
+    try:
+        a = fast_jl.project_normal_32(g, N, 5, T)
+        m = fast_jl._stored[cuda.index]
+        assert (m.F, m.N, m.seed, m.tiles) == (F, N, 5, T)
+        assert torch.equal(a[0], plain[0]) and rel_rows(a.cpu().numpy(), plain.cpu().numpy()) <= 1e-4
+        b = fast_jl.project_normal_8(g[:8].contiguous(), N, 5, T)
+        assert fast_jl._stored[cuda.index] is m                      # the same matrix serves the next batch
+        assert torch.equal(b[0], plain[0]) and rel_rows(b.cpu().numpy(), plain[:8].cpu().numpy()) <= 1e-4
+        c = fast_jl.project_normal_16(g, N, 6, T)                    # next checkpoint: the matrix is replaced
+        assert fast_jl._stored[cuda.index].seed == 6 and len(fast_jl._stored) == 1
+        assert rel_rows(c.cpu().numpy(), ours(g, N, 6, T, NOR).cpu().numpy()) <= 1e-4
+        r = fast_jl.project_rademacher_32(g, N, 5, T)
+        assert fast_jl._stored[cuda.index].seed == 6                 # untouched by the Rademacher entry points
+        assert torch.equal(r, ours(g, N, 5, T, RAD))
+        with pytest.raises(ValueError):
+            fast_jl.project_normal_32(g, 100, 5, T)
+        with pytest.raises(RuntimeError):
+            fast_jl.project_normal_32(g.cpu(), N, 5, T)
+        # a matrix that would not leave the caller its headroom is not stored; the call regenerates as usual
+        monkeypatch.setattr(fast_jl, "_STORE_HEADROOM", 1 << 60)
+        d = fast_jl.project_normal_32(g, N, 7, T)
+        assert cuda.index not in fast_jl._stored and len(fast_jl._does_not_fit) == 1
+        assert torch.equal(d, ours(g, N, 7, T, NOR))
+    finally:
+        fast_jl.store_matrices(False)
+    assert not fast_jl._stored and not fast_jl._does_not_fit
+
+
 def test_bounded_wait_times_out_and_device_stays_usable(cuda):
     """Failure detection without a fault: a wait that nothing satisfies gives up after its limit, the
     status word reports it, and the next call works."""

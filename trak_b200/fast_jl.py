@@ -47,8 +47,9 @@ def _workspace(device, stream, nbytes):
 
 
 def free_workspaces():
-    """Drops the cached per-(device, stream) workspaces."""
+    """Drops the cached per-(device, stream) workspaces and the matrices kept by the stored-matrix mode."""
     _workspaces.clear()
+    _stored.clear()
 
 
 class StoredMatrix:
@@ -210,6 +211,62 @@ def project_segments(tensors, N, seed, num_feature_tiles, proj_type, *, alpha=1.
     return out
 
 
+# ---- opt-in: keep the Gaussian matrix in device memory between calls of the six entry points -----------------
+# The reference's CudaProjector calls project_normal_* once per batch with the same (seed, num_feature_tiles) for a
+# whole checkpoint (trak/projectors.py:414-440).  With TRAK_B200_STORE_MATRIX=1 (or store_matrices(True)) the
+# entry points generate that matrix once per device and read it afterwards (StoredMatrix), when it fits next to
+# what the process already holds; otherwise, and for the Rademacher matrix (cheaper to regenerate than to read),
+# nothing changes.
+_store = os.environ.get("TRAK_B200_STORE_MATRIX", "0") not in ("", "0")
+_stored = {}          # device index -> StoredMatrix (one per device: the matrices are tens of GB)
+_does_not_fit = set()
+_STORE_HEADROOM = 2 << 30   # bytes left to the caller after the matrix is allocated
+
+
+def store_matrices(on: bool = True):
+    """Turns the stored-matrix mode of ``project_normal_*`` on or off; off also frees the matrices."""
+    global _store
+    _store = bool(on)
+    if not _store:
+        _stored.clear()
+        _does_not_fit.clear()
+
+
+def _auto_matrix(input, N, seed, num_feature_tiles):
+    if not (_store and isinstance(input, torch.Tensor) and input.is_cuda and input.dim() == 2
+            and input.dtype in _DTYPES and input.shape[0] > 0 and input.shape[1] > 0):
+        return None   # project() raises the reference's error for it
+    dev = input.device
+    elem = _lib.TB_BF16 if input.dtype == torch.bfloat16 else _lib.TB_F16
+    key = (dev.index, input.shape[1], N, seed, num_feature_tiles, elem)
+    m = _stored.get(dev.index)
+    if m is not None and (dev.index, m.F, m.N, m.seed, m.tiles, m.elem) == key:
+        return m
+    if key in _does_not_fit:
+        return None
+    try:
+        need = StoredMatrix.nbytes(input.shape[1], _u32("N", N), max(_u32("num_feature_tiles", num_feature_tiles), 1))
+        _u32("seed", seed)
+    except TypeError:
+        return None
+    if need == 0:
+        return None
+    _stored.pop(dev.index, None)
+    m = None
+    free, _ = torch.cuda.mem_get_info(dev)
+    free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)   # blocks torch can reuse
+    if need + _STORE_HEADROOM > free:
+        _does_not_fit.add(key)
+        return None
+    try:
+        m = StoredMatrix(input.shape[1], N, seed, num_feature_tiles, _lib.TB_NORMAL, dtype=input.dtype, device=dev)
+    except torch.cuda.OutOfMemoryError:
+        _does_not_fit.add(key)
+        return None
+    _stored[dev.index] = m
+    return m
+
+
 def project_rademacher_8(input, N, seed, num_feature_tiles):
     return project(input, N, seed, num_feature_tiles, _lib.TB_RADEMACHER)
 
@@ -223,12 +280,15 @@ def project_rademacher_32(input, N, seed, num_feature_tiles):
 
 
 def project_normal_8(input, N, seed, num_feature_tiles):
-    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL,
+                   matrix=_auto_matrix(input, N, seed, num_feature_tiles))
 
 
 def project_normal_16(input, N, seed, num_feature_tiles):
-    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL,
+                   matrix=_auto_matrix(input, N, seed, num_feature_tiles))
 
 
 def project_normal_32(input, N, seed, num_feature_tiles):
-    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL)
+    return project(input, N, seed, num_feature_tiles, _lib.TB_NORMAL,
+                   matrix=_auto_matrix(input, N, seed, num_feature_tiles))
