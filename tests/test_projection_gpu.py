@@ -207,6 +207,71 @@ def test_projector_classes(cuda):
     assert got.shape == (6, 1024)
 
 
+def _chunked_like_the_reference_suite(g, proj_dim, seed, proj_type, dtype, cuda, n_chunks):
+    """The projector set-up of the reference's tests/test_jl.py:394-443: the gradient split into column chunks
+    (a dict, one entry per chunk), one CudaProjector per chunk with seeds from default_rng(seed), summed by
+    ChunkedCudaProjector."""
+    from trak_b200.projectors import CudaProjector, ChunkedCudaProjector
+    chunks = dict(enumerate(torch.chunk(g, n_chunks, dim=1)))
+    seeds = np.random.default_rng(seed).integers(low=0, high=500, size=len(chunks))
+    sizes = [v.size(1) for v in chunks.values()]
+    per_chunk = [CudaProjector(grad_dim=sz, proj_dim=proj_dim, seed=int(seeds[i]), proj_type=proj_type,
+                               max_batch_size=32, dtype=dtype, device=cuda) for i, sz in enumerate(sizes)]
+    return ChunkedCudaProjector(per_chunk, max(sizes), sizes, g.shape[0], cuda, dtype), chunks
+
+
+@pytest.mark.parametrize("ptype", ["rademacher", "normal"])
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(1, 25), (8, 10_000), (16, 10_002), (9, 10_002), (45, 1049)])
+def test_properties_of_the_reference_suite(cuda, ptype, dt, shape):
+    """The property tests of the reference's own suite, on its shapes (tests/test_jl.py:46-56), through the same
+    classes: equal rows give equal projections (test_same_features), every output depends on every feature
+    (test_single_nonzero_feature), orthogonal rows stay nearly orthogonal (test_orthogonality), the same seed gives
+    the same projection and another seed another one (test_seed_consistency)."""
+    from trak_b200.projectors import CudaProjector, ProjectionType
+    pt = ProjectionType(ptype)
+    B, F = shape
+    gen = torch.Generator(device=cuda).manual_seed(F + B)
+    for proj_dim in (1024, 4096):
+        g = (torch.rand(B, F, device=cuda, generator=gen) * 2 - 1).to(dt)
+        g[-1] = g[0]
+        proj, chunks = _chunked_like_the_reference_suite(g, proj_dim, 10 ** 8, pt, dt, cuda, n_chunks=min(3, F))
+        p = proj.project(chunks, model_id=0)
+        assert p.shape == (B, proj_dim) and torch.equal(p[0], p[-1])
+        # one non-zero feature per row, anywhere: no output stays zero
+        z = torch.zeros(B, F, device=cuda, dtype=dt)
+        cols = torch.randint(0, F, (B,), generator=torch.Generator().manual_seed(B))
+        z[torch.arange(B), cols] = torch.randn(B, generator=torch.Generator().manual_seed(F)).to(dt).to(cuda) + 2.0
+        single = CudaProjector(grad_dim=F, proj_dim=proj_dim, seed=1, proj_type=pt, device=cuda, max_batch_size=32)
+        q = single.project(z, model_id=0)
+        assert bool((q != 0).all())
+        assert torch.equal(q, single.project(z, model_id=0))
+        other = CudaProjector(grad_dim=F, proj_dim=proj_dim, seed=2, proj_type=pt, device=cuda, max_batch_size=32)
+        assert not torch.equal(q, other.project(z, model_id=0))
+        # (the Rademacher bits of a stream's first draws are the same for seeds 10^4 apart -- a property of the
+        # reference's seeding that the oracle reproduces -- so another model_id is compared on dense rows)
+        if F >= 1000:
+            assert not torch.equal(single.project(g, model_id=0), single.project(g, model_id=1))
+        if B > 1 and F >= 1000:
+            # the reference's criterion (tests/test_jl.py:451-497) is that of ten orthogonal pairs more than a
+            # third project to an inner product below 1e-3; here the cosine itself is bounded.  Gaussian matrix
+            # only: with feature tiles of a few 16-feature chunks (F / 148 features per tile) the Rademacher
+            # matrix consists of the first draws of XORWOW streams whose seeds are in arithmetic progression,
+            # which are strongly correlated -- cosines of 0.3 to 0.4 at these sizes, with the oracle's matrix as
+            # with this kernel's: a property of the matrix definition, which large models (thousands of chunks
+            # per tile) do not show (test_norm_and_inner_product_preservation)
+            if pt != ProjectionType.normal:
+                continue
+            wins, worst = 0, 0.0
+            for _ in range(10):
+                a = torch.rand(B, F, device=cuda, generator=gen) * 2 - 1
+                a[-1] -= (a[0] @ a[-1]) / a[0].norm() ** 2 * a[0]
+                r = single.project(a.to(dt), model_id=0)
+                wins += int(float(r[0] @ r[-1]) < 1e-3)
+                worst = max(worst, abs(float(r[0] @ r[-1] / (r[0].norm() * r[-1].norm()))))
+            assert wins > 0.33 * 10 and worst < 6.0 / proj_dim ** 0.5, (wins, worst)
+
+
 @pytest.mark.parametrize("dt", ["f16", "f32", "bf16"])
 @pytest.mark.parametrize("B", [5, 140])
 def test_segments_equal_concatenation(cuda, dt, B):
