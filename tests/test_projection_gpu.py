@@ -381,6 +381,9 @@ def test_large_feature_count_and_projection_dim(cuda, B, F):
         g[B - 1, f] = coef[i]
     out = ours(g, N, seed, T, RAD)
     del g
+    from trak_b200 import fast_jl
+    fast_jl.free_workspaces()       # tens of GB of staging for these shapes: not kept for the tests that follow
+    torch.cuda.empty_cache()
     key = (F, tuple(feats))
     if key not in _big_rows:
         _big_rows[key] = o.matrix_rows(RAD, F, N, seed, T, feats)
