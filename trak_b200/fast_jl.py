@@ -255,6 +255,8 @@ def _auto_matrix(input, N, seed, num_feature_tiles):
     m = None
     free, _ = torch.cuda.mem_get_info(dev)
     free += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)   # blocks torch can reuse
+    if len(_does_not_fit) > 64:
+        _does_not_fit.clear()
     if need + _STORE_HEADROOM > free:
         _does_not_fit.add(key)
         return None
